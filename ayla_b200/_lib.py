@@ -1,0 +1,204 @@
+"""ctypes loader for ``libayla_b200.so`` and typed wrappers of its C ABI.
+
+This is the counterpart of the reference's PTX launcher runtime
+(ayla/ptx_runtime.py:26-296, :333-446): where that module JIT-loads PTX through a
+``load_inline`` shim, this one ``dlopen``s a prebuilt sm_100a library whose entry
+points are declared in ``include/ayla_b200.h``.  There is no fallback: if the
+library is missing or a call fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+OP_CODES = {"mm": 0, "addmm": 1, "bmm": 2}
+DTYPE_CODES = {"float16": 0, "bfloat16": 1}
+
+E_INVALID, E_UNSUPPORTED, E_WORKSPACE, E_CUDA, E_NOT_INIT = 1, 2, 3, 4, 5
+
+EXPORTS = (
+    "ayla_b200_init",
+    "ayla_b200_gemm",
+    "ayla_b200_swiglu",
+    "ayla_b200_default_config",
+    "ayla_b200_config_valid",
+    "ayla_b200_workspace_bytes",
+    "ayla_b200_workspace_counter_bytes",
+    "ayla_b200_kernel_count",
+    "ayla_b200_kernel_info",
+    "ayla_b200_set_wait_timeout_ms",
+    "ayla_b200_last_error",
+    "ayla_b200_version",
+)
+
+
+class Config(ctypes.Structure):
+    """Mirror of ``struct ayla_b200_config``."""
+
+    _fields_ = [
+        ("tile_n", ctypes.c_int32),
+        ("cta_group", ctypes.c_int32),
+        ("swap_ab", ctypes.c_int32),
+        ("split_k", ctypes.c_int32),
+        ("group_m", ctypes.c_int32),
+        ("grid_ctas", ctypes.c_int32),
+        ("l2_hint_a", ctypes.c_int32),
+        ("l2_hint_b", ctypes.c_int32),
+    ]
+
+    FIELDS = tuple(name for name, _ in _fields_)
+
+    @classmethod
+    def from_dict(cls, values: dict) -> "Config":
+        cfg = cls(tile_n=256, cta_group=1, swap_ab=0, split_k=1, group_m=8, grid_ctas=0,
+                  l2_hint_a=0, l2_hint_b=0)
+        for key in cls.FIELDS:
+            if key in values and values[key] is not None:
+                setattr(cfg, key, int(values[key]))
+        return cfg
+
+    def to_dict(self) -> dict:
+        return {key: int(getattr(self, key)) for key in self.FIELDS}
+
+
+class AylaB200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+_initialised_devices: set[int] = set()
+
+
+def library_path() -> Path:
+    override = os.environ.get("AYLA_B200_LIB")
+    if override:
+        return Path(override)
+    return Path(__file__).resolve().parent / "lib" / "libayla_b200.so"
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and declare the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = library_path()
+        if not path.exists():
+            raise ImportError(
+                f"{path} not found: build it with `python -m ayla_b200.build` "
+                "(there is no non-CUDA fallback)"
+            )
+        lib = ctypes.CDLL(str(path))
+        i32, i64, vp, sz = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
+        cfgp = ctypes.POINTER(Config)
+        lib.ayla_b200_init.argtypes = [i32]
+        lib.ayla_b200_init.restype = i32
+        lib.ayla_b200_gemm.argtypes = [i32, i32, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, sz, vp, vp]
+        lib.ayla_b200_gemm.restype = i32
+        lib.ayla_b200_swiglu.argtypes = [i32, vp, vp, vp, vp, i64, i64, i64, cfgp, vp, vp]
+        lib.ayla_b200_swiglu.restype = i32
+        lib.ayla_b200_default_config.argtypes = [i32, i32, i64, i64, i64, i64, cfgp]
+        lib.ayla_b200_default_config.restype = i32
+        lib.ayla_b200_config_valid.argtypes = [cfgp, i32, i32, i64, i64, i64, i64]
+        lib.ayla_b200_config_valid.restype = i32
+        lib.ayla_b200_workspace_bytes.argtypes = [cfgp, i32, i64, i64, i64, i64]
+        lib.ayla_b200_workspace_bytes.restype = sz
+        lib.ayla_b200_workspace_counter_bytes.argtypes = [cfgp, i32, i64, i64, i64, i64]
+        lib.ayla_b200_workspace_counter_bytes.restype = sz
+        lib.ayla_b200_kernel_count.argtypes = []
+        lib.ayla_b200_kernel_count.restype = i32
+        i32p = ctypes.POINTER(ctypes.c_int32)
+        lib.ayla_b200_kernel_info.argtypes = [i32, i32p, i32p, i32p, i32p, i32p, i32p]
+        lib.ayla_b200_kernel_info.restype = i32
+        lib.ayla_b200_set_wait_timeout_ms.argtypes = [i64]
+        lib.ayla_b200_set_wait_timeout_ms.restype = None
+        lib.ayla_b200_last_error.argtypes = []
+        lib.ayla_b200_last_error.restype = ctypes.c_char_p
+        lib.ayla_b200_version.argtypes = []
+        lib.ayla_b200_version.restype = ctypes.c_char_p
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    return (load().ayla_b200_last_error() or b"").decode()
+
+
+def check(code: int) -> None:
+    """Map a C status code to the exception types the reference raises:
+    ``ValueError`` for argument/shape problems (ayla/jit_compiler.py:76-93,
+    ayla/gemm_jit.py:378-381) and ``RuntimeError`` for CUDA failures
+    (ayla/ptx_runtime.py:41-49)."""
+    if code == 0:
+        return
+    message = last_error()
+    if code in (E_INVALID, E_UNSUPPORTED, E_WORKSPACE):
+        raise ValueError(message)
+    raise AylaB200Error(code, message)
+
+
+def init(device: int) -> None:
+    """Per-device set-up; must first happen outside CUDA-graph capture."""
+    if device in _initialised_devices:
+        return
+    check(load().ayla_b200_init(int(device)))
+    _initialised_devices.add(device)
+
+
+def version() -> str:
+    return load().ayla_b200_version().decode()
+
+
+def kernel_variants() -> list[dict]:
+    lib = load()
+    out = []
+    for i in range(lib.ayla_b200_kernel_count()):
+        vals = [ctypes.c_int32() for _ in range(6)]
+        check(lib.ayla_b200_kernel_info(i, *[ctypes.byref(v) for v in vals]))
+        keys = ("tile_n", "cta_group", "epilogue", "transposed_out", "stages", "smem_bytes")
+        out.append({k: v.value for k, v in zip(keys, vals)})
+    return out
+
+
+def default_config(op: str, dtype: str, batch: int, m: int, n: int, k: int) -> Config:
+    cfg = Config()
+    check(load().ayla_b200_default_config(OP_CODES[op], DTYPE_CODES[dtype], batch, m, n, k,
+                                          ctypes.byref(cfg)))
+    return cfg
+
+
+def config_valid(cfg: Config, op: str, dtype: str, batch: int, m: int, n: int, k: int) -> bool:
+    return load().ayla_b200_config_valid(ctypes.byref(cfg), OP_CODES[op], DTYPE_CODES[dtype],
+                                         batch, m, n, k) == 0
+
+
+def workspace_bytes(cfg: Config, op: str, batch: int, m: int, n: int, k: int) -> int:
+    return int(load().ayla_b200_workspace_bytes(ctypes.byref(cfg), OP_CODES[op], batch, m, n, k))
+
+
+def workspace_counter_bytes(cfg: Config, op: str, batch: int, m: int, n: int, k: int) -> int:
+    return int(load().ayla_b200_workspace_counter_bytes(ctypes.byref(cfg), OP_CODES[op], batch, m, n, k))
+
+
+def gemm(op: str, dtype: str, bias_ptr: int, a_ptr: int, bt_ptr: int, out_ptr: int, batch: int,
+         m: int, n: int, k: int, cfg: Config | None, workspace_ptr: int, workspace_size: int,
+         status_ptr: int, stream: int) -> None:
+    check(load().ayla_b200_gemm(
+        OP_CODES[op], DTYPE_CODES[dtype], bias_ptr or None, a_ptr, bt_ptr, out_ptr, batch, m, n, k,
+        ctypes.byref(cfg) if cfg is not None else None, workspace_ptr or None, workspace_size,
+        status_ptr or None, stream or None))
+
+
+def swiglu(dtype: str, x_ptr: int, wg_ptr: int, wu_ptr: int, out_ptr: int, m: int, n: int, k: int,
+           cfg: Config | None, status_ptr: int, stream: int) -> None:
+    check(load().ayla_b200_swiglu(
+        DTYPE_CODES[dtype], x_ptr, wg_ptr, wu_ptr, out_ptr, m, n, k,
+        ctypes.byref(cfg) if cfg is not None else None, status_ptr or None, stream or None))

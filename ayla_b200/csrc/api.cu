@@ -1,0 +1,631 @@
+// C ABI of the sm_100a GEMM backend: argument checks, schedule choice, tensor-map
+// encoding and the kernel launch.  Nothing here allocates device memory or
+// synchronises, so every entry point except ayla_b200_init can run inside CUDA
+// graph capture.
+#include "../../include/ayla_b200.h"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "kernel_registry.h"
+
+namespace ayla_b200 {
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+constexpr int kMaxVariants = 64;
+constexpr int kMaxDevices = 64;
+
+struct Registry {
+  KernelEntry entries[kMaxVariants];
+  int count = 0;
+  Registry() {
+    append_variants_cg1(entries, &count);
+    append_variants_cg2(entries, &count);
+    append_variants_trans(entries, &count);
+    append_variants_swiglu(entries, &count);
+  }
+  const KernelEntry* find(int tile_n, int cta_group, int epilogue, int transposed) const {
+    for (int i = 0; i < count; ++i) {
+      const KernelEntry& e = entries[i];
+      if (e.tile_n == tile_n && e.cta_group == cta_group && e.epilogue == epilogue &&
+          e.transposed_out == transposed) {
+        return &e;
+      }
+    }
+    return nullptr;
+  }
+};
+
+const Registry& registry() {
+  static const Registry r;
+  return r;
+}
+
+struct DeviceState {
+  std::atomic<bool> ready{false};
+  int sm_count = 0;
+};
+DeviceState g_devices[kMaxDevices];
+std::mutex g_init_mutex;
+PFN_cuTensorMapEncodeTiled g_encode_tiled = nullptr;
+std::atomic<long long> g_timeout_ns{2000000000ll};
+
+// ------------------------------------------------------------- tensor maps
+
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, d2;
+  uint32_t b0, b1, b2;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && b0 == o.b0 && b1 == o.b1 &&
+           b2 == o.b2;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.d0 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.d1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.d2 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= ((static_cast<uint64_t>(k.b0) << 40) ^ (static_cast<uint64_t>(k.b1) << 20) ^ k.b2) +
+         (h << 6) + (h >> 2);
+    return static_cast<size_t>(h);
+  }
+};
+
+// Descriptors are pure functions of (pointer, extents, box); cache them by value
+// as the reference's launcher does (ayla/ptx_runtime.py:185-235), behind a mutex
+// because this library does not rely on the GIL.
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+std::mutex g_map_mutex;
+
+// 3-D map over a row-major [d2][d1][d0] tensor of 16-bit elements, box
+// [b2][b1][b0], 128-byte swizzle (b0 must be 64 elements).
+int encode_map(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0,
+               uint32_t b1, uint32_t b2) {
+  const MapKey key{ptr, d0, d1, d2, b0, b1, b2};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) {
+      *out = it->second;
+      return AYLA_B200_OK;
+    }
+  }
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  const cuuint32_t box[3] = {b0, b1, b2};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = g_encode_tiled(
+      out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(AYLA_B200_E_CUDA,
+                "cuTensorMapEncodeTiled failed (%d) for ptr=%p dims=[%llu,%llu,%llu] box=[%u,%u,%u]",
+                static_cast<int>(r), ptr, (unsigned long long)d0, (unsigned long long)d1,
+                (unsigned long long)d2, b0, b1, b2);
+  }
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache.size() > 8192) g_map_cache.clear();
+  g_map_cache.emplace(key, *out);
+  return AYLA_B200_OK;
+}
+
+// ------------------------------------------------------------ the schedule
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// The problem as the kernel sees it after an optional swap of the operands.
+struct Problem {
+  int64_t rows, cols, k, batch;  // rows fill the 128-row tile, cols the accumulator width
+  const void* row_operand;       // [batch][rows][k]
+  const void* col_operand;       // [batch][cols][k]
+};
+
+struct Plan {
+  const KernelEntry* kernel;
+  int m_tiles, n_tiles, k_blocks, splits, kb_per_split, total_units, group_m, grid;
+  int row_tiles;  // 128-row x tile_n tiles (split-K counters, slabs)
+};
+
+int check_shape(int op, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
+  if (op != AYLA_B200_OP_MM && op != AYLA_B200_OP_ADDMM && op != AYLA_B200_OP_BMM) {
+    return fail(AYLA_B200_E_INVALID, "unknown op %d", op);
+  }
+  if (dtype != AYLA_B200_F16 && dtype != AYLA_B200_BF16) {
+    return fail(AYLA_B200_E_INVALID, "unknown dtype %d (0 = float16, 1 = bfloat16)", dtype);
+  }
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) {
+    return fail(AYLA_B200_E_INVALID, "non-positive extent batch=%lld m=%lld n=%lld k=%lld",
+                (long long)batch, (long long)m, (long long)n, (long long)k);
+  }
+  if (op != AYLA_B200_OP_BMM && batch != 1) {
+    return fail(AYLA_B200_E_INVALID, "batch must be 1 for mm/addmm, got %lld", (long long)batch);
+  }
+  if (n % 8 != 0) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "n=%lld must be a multiple of 8 (16-byte output rows)",
+                (long long)n);
+  }
+  if (k % 8 != 0) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "k=%lld must be a multiple of 8 (16-byte operand rows)",
+                (long long)k);
+  }
+  if (m > 0x7FFFFFFF / 2 || n > 0x7FFFFFFF / 2 || k > 0x7FFFFFFF / 2 || batch > 65535 * 16) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "extent too large for 32-bit tile coordinates");
+  }
+  return AYLA_B200_OK;
+}
+
+int check_config(const ayla_b200_config& c, bool swiglu) {
+  if (c.cta_group != 1 && c.cta_group != 2) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "cta_group must be 1 or 2, got %d", c.cta_group);
+  }
+  if (c.split_k < 1 || c.group_m < 1 || c.grid_ctas < 0) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "split_k and group_m must be >= 1, grid_ctas >= 0");
+  }
+  if (c.l2_hint_a < 0 || c.l2_hint_a > 2 || c.l2_hint_b < 0 || c.l2_hint_b > 2) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "L2 hints must be 0, 1 or 2");
+  }
+  if (swiglu) {
+    if (c.split_k != 1 || c.swap_ab != 0) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "the SwiGLU kernel has no split-K or swapped form");
+    }
+    return AYLA_B200_OK;
+  }
+  if (c.swap_ab) {
+    if (c.cta_group != 1) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "swap_ab is only built with cta_group == 1");
+    }
+    if (c.tile_n != 16 && c.tile_n != 32 && c.tile_n != 64 && c.tile_n != 128) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "swap_ab needs tile_n in {16,32,64,128}, got %d", c.tile_n);
+    }
+  } else if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "tile_n must be 64, 128 or 256, got %d", c.tile_n);
+  }
+  return AYLA_B200_OK;
+}
+
+// Fills `plan` for a validated config.  `epilogue` is one of EPI_*.
+int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t rows, int64_t cols,
+              int64_t k, int sm_count, Plan* plan) {
+  const int transposed = c.swap_ab ? 1 : 0;
+  const int tile_n = (epilogue == EPI_SWIGLU) ? 256 : c.tile_n;
+  const KernelEntry* e = registry().find(tile_n, c.cta_group, epilogue, transposed);
+  if (e == nullptr) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "no kernel variant tile_n=%d cta_group=%d epilogue=%d swap=%d",
+                tile_n, c.cta_group, epilogue, transposed);
+  }
+  const int out_tile_n = (epilogue == EPI_SWIGLU) ? 128 : tile_n;
+  plan->kernel = e;
+  plan->m_tiles = static_cast<int>(ceil_div(rows, 128 * c.cta_group));
+  plan->n_tiles = static_cast<int>(ceil_div(cols, out_tile_n));
+  plan->k_blocks = static_cast<int>(ceil_div(k, 64));
+  int splits = c.split_k;
+  if (splits > plan->k_blocks) splits = plan->k_blocks;
+  plan->kb_per_split = static_cast<int>(ceil_div(plan->k_blocks, splits));
+  plan->splits = static_cast<int>(ceil_div(plan->k_blocks, plan->kb_per_split));
+  const int64_t tiles = static_cast<int64_t>(batch) * plan->m_tiles * plan->n_tiles;
+  const int64_t units = tiles * plan->splits;
+  if (units > 0x7FFFFFFF || tiles * c.cta_group > 0x7FFFFFFF) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "too many tiles (%lld)", (long long)units);
+  }
+  plan->total_units = static_cast<int>(units);
+  plan->row_tiles = static_cast<int>(tiles * c.cta_group);
+  plan->group_m = c.group_m;
+  int grid = (c.grid_ctas > 0) ? c.grid_ctas : sm_count;
+  if (c.cta_group == 2) {
+    grid &= ~1;
+    if (grid < 2) grid = 2;
+    if (static_cast<int64_t>(grid / 2) > units) grid = static_cast<int>(2 * units);
+  } else {
+    if (grid < 1) grid = 1;
+    if (static_cast<int64_t>(grid) > units) grid = static_cast<int>(units);
+  }
+  plan->grid = grid;
+  return AYLA_B200_OK;
+}
+
+size_t counter_bytes_for(const Plan& p) {
+  if (p.splits <= 1) return 0;
+  return (static_cast<size_t>(p.row_tiles) * 4 + 255) & ~static_cast<size_t>(255);
+}
+
+size_t workspace_bytes_for(const Plan& p) {
+  if (p.splits <= 1) return 0;
+  return counter_bytes_for(p) +
+         static_cast<size_t>(p.row_tiles) * p.splits * 128 * p.kernel->tile_n * sizeof(float);
+}
+
+uint32_t make_idesc(int is_bf16, int mma_m, int mma_n) {
+  // tcgen05 .kind::f16 instruction descriptor: fp32 accumulator (bits 4-5 = 1),
+  // A/B element format (bits 7-9 / 10-12: 0 = f16, 1 = bf16), both operands
+  // K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+  uint32_t d = 0;
+  d |= 1u << 4;
+  d |= static_cast<uint32_t>(is_bf16 ? 1 : 0) << 7;
+  d |= static_cast<uint32_t>(is_bf16 ? 1 : 0) << 10;
+  d |= static_cast<uint32_t>(mma_n >> 3) << 17;
+  d |= static_cast<uint32_t>(mma_m >> 4) << 24;
+  return d;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int current_device_state(DeviceState** out, int* device) {
+  int dev = -1;
+  const cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) {
+    return fail(AYLA_B200_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(err));
+  }
+  if (dev < 0 || dev >= kMaxDevices || !g_devices[dev].ready.load(std::memory_order_acquire)) {
+    return fail(AYLA_B200_E_NOT_INIT, "ayla_b200_init(%d) has not been called", dev);
+  }
+  *out = &g_devices[dev];
+  *device = dev;
+  return AYLA_B200_OK;
+}
+
+void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count,
+                    ayla_b200_config* c) {
+  memset(c, 0, sizeof(*c));
+  c->cta_group = 1;
+  c->split_k = 1;
+  c->group_m = 8;
+  const int64_t k_blocks = ceil_div(k, 64);
+  if (m <= 64 && n >= 128) {
+    // Weight-streaming regime: put bt's rows on the 128-row tile and M on the
+    // narrow accumulator, then split K until every SM has a share of the stream.
+    c->swap_ab = 1;
+    c->tile_n = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    const int64_t tiles = batch * ceil_div(n, 128);
+    if (tiles < sm_count) {
+      int64_t s = sm_count / tiles;
+      const int64_t max_s = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
+      if (s > max_s) s = max_s;
+      if (s < 1) s = 1;
+      c->split_k = static_cast<int32_t>(s);
+    }
+    c->group_m = 1;
+    return;
+  }
+  // Widest tile that still gives every SM work; pair CTAs when the tile count allows.
+  const int widths[3] = {256, 128, 64};
+  int tile_n = 64;
+  for (int i = 0; i < 3; ++i) {
+    const int w = widths[i];
+    if (n < w && w > 64) continue;
+    const int64_t tiles = batch * ceil_div(m, 128) * ceil_div(n, w);
+    if (tiles >= sm_count || w == 64) {
+      tile_n = w;
+      break;
+    }
+  }
+  c->tile_n = tile_n;
+  const int64_t tiles = batch * ceil_div(m, 128) * ceil_div(n, tile_n);
+  if (m >= 256 && tiles >= 2 * static_cast<int64_t>(sm_count)) c->cta_group = 2;
+  if (tiles * 2 <= sm_count && k_blocks >= 16) {
+    int64_t s = sm_count / tiles;
+    const int64_t max_s = k_blocks / 8;
+    if (s > max_s) s = max_s;
+    if (s < 1) s = 1;
+    c->split_k = static_cast<int32_t>(s);
+  }
+}
+
+int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, int is_bf16,
+                const void* bias, const void* b2_operand, void* out, int64_t out_rows,
+                int64_t out_cols, void* workspace, size_t workspace_bytes, uint32_t* status,
+                cudaStream_t stream) {
+  const KernelEntry& e = *plan.kernel;
+  LaunchArgs la;
+  memset(&la, 0, sizeof(la));
+  const int b_box_rows = (e.epilogue == EPI_SWIGLU) ? 128 : e.tile_n / e.cta_group;
+  int rc = encode_map(&la.tm_a, pr.row_operand, pr.k, pr.rows, pr.batch, 64, 128, 1);
+  if (rc) return rc;
+  rc = encode_map(&la.tm_b, pr.col_operand, pr.k, pr.cols, pr.batch, 64, b_box_rows, 1);
+  if (rc) return rc;
+  if (e.epilogue == EPI_SWIGLU) {
+    rc = encode_map(&la.tm_b2, b2_operand, pr.k, pr.cols, pr.batch, 64, b_box_rows, 1);
+    if (rc) return rc;
+  } else {
+    la.tm_b2 = la.tm_b;
+  }
+  if (!e.transposed_out) {
+    rc = encode_map(&la.tm_d, out, out_cols, out_rows, pr.batch, 64, 32, 1);
+    if (rc) return rc;
+  } else {
+    la.tm_d = la.tm_a;
+  }
+
+  KernelParams& p = la.p;
+  p.m = static_cast<int>(pr.rows);
+  p.n = static_cast<int>(pr.cols);
+  p.k = static_cast<int>(pr.k);
+  p.batch = static_cast<int>(pr.batch);
+  p.m_tiles = plan.m_tiles;
+  p.n_tiles = plan.n_tiles;
+  p.k_blocks = plan.k_blocks;
+  p.splits = plan.splits;
+  p.kb_per_split = plan.kb_per_split;
+  p.total_units = plan.total_units;
+  p.group_m = plan.group_m;
+  p.is_bf16 = is_bf16;
+  p.idesc = make_idesc(is_bf16, 128 * e.cta_group, e.tile_n);
+  // Hints are given for a/bt as the caller passed them.
+  p.l2_hint_a = static_cast<uint32_t>(c.swap_ab ? c.l2_hint_b : c.l2_hint_a);
+  p.l2_hint_b = static_cast<uint32_t>(c.swap_ab ? c.l2_hint_a : c.l2_hint_b);
+  p.bias = bias;
+  p.out = out;
+  p.out_ld = out_cols;               // direct stores: out[batch][col][row], row-major [M][N]
+  p.out_batch_stride = out_rows * out_cols;
+  p.status = status;
+  p.timeout_ns = static_cast<unsigned long long>(g_timeout_ns.load());
+  if (plan.splits > 1) {
+    const size_t need = workspace_bytes_for(plan);
+    if (workspace == nullptr || workspace_bytes < need) {
+      return fail(AYLA_B200_E_WORKSPACE, "split_k=%d needs a workspace of %zu bytes, got %zu",
+                  plan.splits, need, workspace == nullptr ? size_t(0) : workspace_bytes);
+    }
+    if (!aligned16(workspace)) {
+      return fail(AYLA_B200_E_INVALID, "workspace must be 16-byte aligned");
+    }
+    p.counters = reinterpret_cast<unsigned*>(workspace);
+    p.ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + counter_bytes_for(plan));
+  }
+  la.grid = plan.grid;
+  la.stream = stream;
+  const cudaError_t err = e.launch(la);
+  if (err != cudaSuccess) {
+    return fail(AYLA_B200_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(err));
+  }
+  return AYLA_B200_OK;
+}
+
+}  // namespace
+}  // namespace ayla_b200
+
+using namespace ayla_b200;
+
+extern "C" {
+
+int ayla_b200_init(int device) {
+  if (device < 0 || device >= kMaxDevices) {
+    return fail(AYLA_B200_E_INVALID, "device %d out of range", device);
+  }
+  std::lock_guard<std::mutex> lock(g_init_mutex);
+  if (g_devices[device].ready.load(std::memory_order_acquire)) return AYLA_B200_OK;
+  int prev = -1;
+  cudaError_t err = cudaGetDevice(&prev);
+  if (err != cudaSuccess) return fail(AYLA_B200_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(err));
+  err = cudaSetDevice(device);
+  if (err != cudaSuccess) return fail(AYLA_B200_E_CUDA, "cudaSetDevice: %s", cudaGetErrorString(err));
+  int rc = AYLA_B200_OK;
+  do {
+    cudaDeviceProp prop;
+    err = cudaGetDeviceProperties(&prop, device);
+    if (err != cudaSuccess) {
+      rc = fail(AYLA_B200_E_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(err));
+      break;
+    }
+    if (prop.major != 10) {
+      rc = fail(AYLA_B200_E_UNSUPPORTED, "device %d is sm_%d%d; this library is sm_100a only", device,
+                prop.major, prop.minor);
+      break;
+    }
+    if (g_encode_tiled == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+      if (err != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+        rc = fail(AYLA_B200_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+        break;
+      }
+      g_encode_tiled = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    }
+    const Registry& reg = registry();
+    for (int i = 0; i < reg.count; ++i) {
+      const KernelEntry& e = reg.entries[i];
+      err = cudaFuncSetAttribute(e.func, cudaFuncAttributeMaxDynamicSharedMemorySize, e.smem_bytes);
+      if (err != cudaSuccess) {
+        rc = fail(AYLA_B200_E_CUDA, "cudaFuncSetAttribute(smem=%d) for variant %d: %s", e.smem_bytes, i,
+                  cudaGetErrorString(err));
+        break;
+      }
+    }
+    if (rc) break;
+    g_devices[device].sm_count = prop.multiProcessorCount;
+    g_devices[device].ready.store(true, std::memory_order_release);
+  } while (false);
+  if (prev >= 0 && prev != device) cudaSetDevice(prev);
+  return rc;
+}
+
+int ayla_b200_default_config(int op, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                             ayla_b200_config* cfg_out) {
+  if (cfg_out == nullptr) return fail(AYLA_B200_E_INVALID, "cfg_out is null");
+  const int rc = check_shape(op, dtype, batch, m, n, k);
+  if (rc) return rc;
+  int sm_count = 148;
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices &&
+      g_devices[dev].ready.load(std::memory_order_acquire)) {
+    sm_count = g_devices[dev].sm_count;
+  } else {
+    (void)cudaGetLastError();
+  }
+  default_config(batch, m, n, k, sm_count, cfg_out);
+  return AYLA_B200_OK;
+}
+
+int ayla_b200_config_valid(const ayla_b200_config* cfg, int op, int dtype, int64_t batch, int64_t m,
+                           int64_t n, int64_t k) {
+  if (cfg == nullptr) return fail(AYLA_B200_E_INVALID, "cfg is null");
+  int rc = check_shape(op, dtype, batch, m, n, k);
+  if (rc) return rc;
+  rc = check_config(*cfg, false);
+  if (rc) return rc;
+  Plan plan;
+  const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
+  return make_plan(*cfg, epi, batch, cfg->swap_ab ? n : m, cfg->swap_ab ? m : n, k, 148, &plan);
+}
+
+size_t ayla_b200_workspace_bytes(const ayla_b200_config* cfg, int op, int64_t batch, int64_t m,
+                                 int64_t n, int64_t k) {
+  if (cfg == nullptr || check_config(*cfg, false) != AYLA_B200_OK) return 0;
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
+  Plan plan;
+  const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
+  if (make_plan(*cfg, epi, batch, cfg->swap_ab ? n : m, cfg->swap_ab ? m : n, k, 148, &plan)) return 0;
+  return workspace_bytes_for(plan);
+}
+
+size_t ayla_b200_workspace_counter_bytes(const ayla_b200_config* cfg, int op, int64_t batch,
+                                         int64_t m, int64_t n, int64_t k) {
+  if (cfg == nullptr || check_config(*cfg, false) != AYLA_B200_OK) return 0;
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
+  Plan plan;
+  const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
+  if (make_plan(*cfg, epi, batch, cfg->swap_ab ? n : m, cfg->swap_ab ? m : n, k, 148, &plan)) return 0;
+  return counter_bytes_for(plan);
+}
+
+int ayla_b200_gemm(int op, int dtype, const void* bias, const void* a, const void* bt, void* out,
+                   int64_t batch, int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg,
+                   void* workspace, size_t workspace_bytes, uint32_t* status, void* stream) {
+  int rc = check_shape(op, dtype, batch, m, n, k);
+  if (rc) return rc;
+  if (a == nullptr || bt == nullptr || out == nullptr) {
+    return fail(AYLA_B200_E_INVALID, "a, bt and out must be non-null");
+  }
+  if (op == AYLA_B200_OP_ADDMM && bias == nullptr) {
+    return fail(AYLA_B200_E_INVALID, "addmm needs a bias pointer");
+  }
+  if (!aligned16(a) || !aligned16(bt) || !aligned16(out)) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "a, bt and out must be 16-byte aligned");
+  }
+  DeviceState* ds = nullptr;
+  int dev = -1;
+  rc = current_device_state(&ds, &dev);
+  if (rc) return rc;
+
+  ayla_b200_config c;
+  if (cfg != nullptr) {
+    c = *cfg;
+  } else {
+    default_config(batch, m, n, k, ds->sm_count, &c);
+  }
+  rc = check_config(c, false);
+  if (rc) return rc;
+
+  Problem pr;
+  pr.k = k;
+  pr.batch = batch;
+  if (c.swap_ab) {
+    pr.rows = n;
+    pr.cols = m;
+    pr.row_operand = bt;
+    pr.col_operand = a;
+  } else {
+    pr.rows = m;
+    pr.cols = n;
+    pr.row_operand = a;
+    pr.col_operand = bt;
+  }
+  const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
+  Plan plan;
+  rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan);
+  if (rc) return rc;
+  return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, workspace,
+                     workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ayla_b200_swiglu(int dtype, const void* x, const void* w_gate, const void* w_up, void* out,
+                     int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg, uint32_t* status,
+                     void* stream) {
+  int rc = check_shape(AYLA_B200_OP_MM, dtype, 1, m, n, k);
+  if (rc) return rc;
+  if (x == nullptr || w_gate == nullptr || w_up == nullptr || out == nullptr) {
+    return fail(AYLA_B200_E_INVALID, "x, w_gate, w_up and out must be non-null");
+  }
+  if (!aligned16(x) || !aligned16(w_gate) || !aligned16(w_up) || !aligned16(out)) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "x, w_gate, w_up and out must be 16-byte aligned");
+  }
+  DeviceState* ds = nullptr;
+  int dev = -1;
+  rc = current_device_state(&ds, &dev);
+  if (rc) return rc;
+  ayla_b200_config c;
+  if (cfg != nullptr) {
+    c = *cfg;
+  } else {
+    memset(&c, 0, sizeof(c));
+    c.cta_group = (m >= 256) ? 2 : 1;
+    c.group_m = 8;
+  }
+  c.tile_n = 256;
+  c.split_k = 1;
+  c.swap_ab = 0;
+  rc = check_config(c, true);
+  if (rc) return rc;
+  Problem pr;
+  pr.rows = m;
+  pr.cols = n;
+  pr.k = k;
+  pr.batch = 1;
+  pr.row_operand = x;
+  pr.col_operand = w_gate;
+  Plan plan;
+  rc = make_plan(c, EPI_SWIGLU, 1, m, n, k, ds->sm_count, &plan);
+  if (rc) return rc;
+  return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, nullptr, w_up, out, m, n, nullptr, 0,
+                     status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ayla_b200_kernel_count(void) { return registry().count; }
+
+int ayla_b200_kernel_info(int i, int32_t* tile_n, int32_t* cta_group, int32_t* epilogue,
+                          int32_t* transposed_out, int32_t* stages, int32_t* smem_bytes) {
+  const Registry& reg = registry();
+  if (i < 0 || i >= reg.count) return fail(AYLA_B200_E_INVALID, "variant index %d out of range", i);
+  const KernelEntry& e = reg.entries[i];
+  if (tile_n) *tile_n = e.tile_n;
+  if (cta_group) *cta_group = e.cta_group;
+  if (epilogue) *epilogue = e.epilogue;
+  if (transposed_out) *transposed_out = e.transposed_out;
+  if (stages) *stages = e.stages;
+  if (smem_bytes) *smem_bytes = e.smem_bytes;
+  return AYLA_B200_OK;
+}
+
+void ayla_b200_set_wait_timeout_ms(int64_t ms) {
+  if (ms < 1) ms = 1;
+  g_timeout_ns.store(ms * 1000000ll);
+}
+
+const char* ayla_b200_last_error(void) { return g_last_error.c_str(); }
+
+const char* ayla_b200_version(void) { return "ayla_b200 0.1 (sm_100a, tcgen05)"; }
+
+}  // extern "C"

@@ -1,0 +1,610 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   D[b, m, n] = epilogue( sum_k A[b, m, k] * B[b, n, k] )      (both operands K-major)
+//
+// which is the `out = a @ bt.T` convention of the reference's mm/addmm/bmm ops
+// (ayla/gemm_jit.py:267-307): fp16/bf16 inputs, fp32 accumulation, one rounding
+// to the output type at the end (ayla/passes/lower_to_ptx_template.py:134-149).
+//
+// One CTA = 6 warps:
+//   warp 0      TMA producer  : global -> shared ring of STAGES (A 128x64, B BNx64) slabs
+//   warp 1      MMA issuer    : tcgen05.mma from shared into a TMEM accumulator;
+//                               also owns the TMEM allocation
+//   warps 2..5  epilogue      : TMEM -> registers -> (bias | SiLU*up) -> round ->
+//                               swizzled shared -> TMA store   (or direct stores for the
+//                               transposed / split-K forms)
+// The accumulator is double buffered in TMEM so the epilogue of one tile runs
+// under the main loop of the next.  CTAs are persistent and walk a static,
+// M-grouped raster over (batch, m-tile, n-tile, k-split) work units.
+//
+// CTA_GROUP == 2 pairs two CTAs (cluster of 2) on one 256-row tile: each CTA
+// loads its own 128 rows of A and its own half of the B tile with ordinary TMA
+// loads, the leader CTA issues tcgen05.mma.cta_group::2 for both.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "sm100_prims.cuh"
+
+namespace ayla_b200 {
+
+enum : int { EPI_PLAIN = 0, EPI_BIAS = 1, EPI_SWIGLU = 2 };
+
+// Error codes written to the device status word (first error wins).
+enum : unsigned {
+  ST_OK = 0,
+  ST_TIMEOUT_EMPTY = 1,      // producer waited for a free ring slot
+  ST_TIMEOUT_FULL = 2,       // MMA warp waited for operands
+  ST_TIMEOUT_ACC_EMPTY = 3,  // MMA warp waited for a drained accumulator
+  ST_TIMEOUT_ACC_FULL = 4,   // epilogue waited for a finished accumulator
+  ST_BAD_SMEM_ALIGN = 5,
+};
+
+struct KernelParams {
+  int m, n, k;        // extents of the kernel's (row, column, depth) problem
+  int batch;
+  int m_tiles;        // tiles of 128*CTA_GROUP rows
+  int n_tiles;        // tiles of the output tile width
+  int k_blocks;       // ceil(k / 64)
+  int splits;         // k-splits per tile (1 = none)
+  int kb_per_split;
+  int total_units;    // batch * m_tiles * n_tiles * splits
+  int group_m;        // raster: m-tiles per group
+  int is_bf16;        // output / operand type: 1 bf16, 0 fp16
+  uint32_t idesc;     // tcgen05 instruction descriptor
+  uint32_t l2_hint_a; // 0 normal, 1 evict_first, 2 evict_last
+  uint32_t l2_hint_b;
+  const void* bias;   // [n] (or [m] when the output is transposed)
+  void* out;          // used by the direct-store epilogues
+  long long out_ld;   // leading dimension of `out` in elements (direct stores)
+  long long out_batch_stride;
+  float* ws;          // split-K partial slabs
+  unsigned* counters; // split-K arrival counters, one per 128-row tile; zero between launches
+  unsigned* status;   // optional device status word (may be null)
+  unsigned long long timeout_ns;
+};
+
+template <int BN_, int CTA_GROUP_, int EPI_, bool TRANS_OUT_, int STAGES_>
+struct GemmTraits {
+  static constexpr int BN = BN_;                // MMA N (accumulator columns)
+  static constexpr int CTA_GROUP = CTA_GROUP_;
+  static constexpr int EPI = EPI_;
+  static constexpr bool TRANS_OUT = TRANS_OUT_;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int BM = 128;                // rows per CTA
+  static constexpr int BK = 64;                 // one 128-byte swizzle atom of 16-bit elements
+  static constexpr int OUT_BN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;  // output tile width
+  static constexpr int B_ROWS = BN / CTA_GROUP; // B rows this CTA loads per stage
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int ACC_BUFS = 2;
+  static constexpr int TMEM_COLS_NEEDED = ACC_BUFS * BN;
+  static constexpr int TMEM_COLS = TMEM_COLS_NEEDED <= 32    ? 32
+                                   : TMEM_COLS_NEEDED <= 64  ? 64
+                                   : TMEM_COLS_NEEDED <= 128 ? 128
+                                   : TMEM_COLS_NEEDED <= 256 ? 256
+                                                             : 512;
+  static constexpr int EPI_WARPS = 4;
+  static constexpr int STORE_BUF_BYTES = 32 * 128;  // 32 rows x 64 columns of 16-bit
+  static constexpr int STORE_BYTES = TRANS_OUT ? 0 : EPI_WARPS * 2 * STORE_BUF_BYTES;
+  static constexpr int BIAS_BYTES = (EPI == EPI_BIAS && !TRANS_OUT) ? 2 * BN * 4 : 0;
+  static constexpr int MISC_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BIAS_BYTES + MISC_BYTES;
+  static constexpr int THREADS = 192;
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05 N extent");
+  static_assert(B_BYTES % 1024 == 0, "B slab must keep the 1024-byte swizzle alignment");
+  static_assert(EPI != EPI_SWIGLU || (BN == 256 && !TRANS_OUT), "SwiGLU uses the 2x128 layout");
+  static_assert(TRANS_OUT || BN >= 64, "the TMA-store epilogue writes 64-column boxes");
+  static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
+  static_assert((2 * STAGES + 2 * ACC_BUFS) * 8 + 16 <= MISC_BYTES, "barrier area too small");
+};
+
+// A wait that gives up: polls the barrier, and every few thousand polls checks a
+// CTA-wide abort flag and the global timer.  After a timeout the first error
+// code is published, the abort flag is raised and every later wait in the CTA
+// returns at once, so the kernel always terminates.
+struct BoundedWait {
+  volatile uint32_t* abort_flag;
+  unsigned* status;
+  unsigned long long timeout_ns;
+
+  __device__ __forceinline__ bool aborted() const { return *abort_flag != 0; }
+
+  __device__ __noinline__ void give_up(unsigned code) const {
+    *abort_flag = 1;
+    if (status != nullptr) atomicCAS(status, 0u, code | (blockIdx.x << 8));
+  }
+
+  __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity, unsigned code) const {
+    if (mbar_try_wait(bar, parity)) return;
+    if (aborted()) return;
+    uint64_t t0 = 0;
+    uint32_t polls = 0;
+    while (!mbar_try_wait(bar, parity)) {
+      if ((++polls & 0x3F) == 0) {
+        if (aborted()) return;
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > timeout_ns) {
+          give_up(code);
+          return;
+        }
+      }
+    }
+  }
+};
+
+struct WorkUnit {
+  int batch, m0, n0, kb0, kb1, split, row_tile;
+};
+
+template <class T>
+__device__ __forceinline__ WorkUnit decode_unit(const KernelParams& p, int unit, int cta_rank) {
+  WorkUnit w;
+  const int split = unit % p.splits;
+  int tile = unit / p.splits;
+  const int tiles_per_batch = p.m_tiles * p.n_tiles;
+  w.batch = tile / tiles_per_batch;
+  const int t = tile - w.batch * tiles_per_batch;
+  const int group_size = p.group_m * p.n_tiles;
+  const int g = t / group_size;
+  const int first_m = g * p.group_m;
+  const int rows_in_group = min(p.m_tiles - first_m, p.group_m);
+  const int r = t - g * group_size;
+  const int m_t = first_m + r % rows_in_group;
+  const int n_t = r / rows_in_group;
+  w.m0 = (m_t * T::CTA_GROUP + cta_rank) * T::BM;
+  w.n0 = n_t * T::OUT_BN;
+  w.split = split;
+  w.kb0 = split * p.kb_per_split;
+  w.kb1 = min(p.k_blocks, w.kb0 + p.kb_per_split);
+  w.row_tile = (w.batch * p.m_tiles + m_t) * T::CTA_GROUP + cta_rank;  // 128-row tile id
+  w.row_tile = w.row_tile * p.n_tiles + n_t;
+  return w;
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
+  if (is_bf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float load_elem(const void* base, long long i, int is_bf16) {
+  if (is_bf16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
+  return __half2float(reinterpret_cast<const __half*>(base)[i]);
+}
+
+__device__ __forceinline__ void store_elem(void* base, long long i, float v, int is_bf16) {
+  if (is_bf16) {
+    reinterpret_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v);
+  } else {
+    reinterpret_cast<__half*>(base)[i] = __float2half_rn(v);
+  }
+}
+
+// silu(g) * u on fp32 accumulators, before the single rounding; same order of
+// operations as the reference's silu lowering (x * 1/(1+2^(-x*log2e)),
+// ayla/passes/lower_to_ptx_template.py:296-315).
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float e = exp2f(-g * 1.4426950408889634f);
+  return __fdividef(g, 1.0f + e) * u;
+}
+
+__device__ __forceinline__ uint64_t make_policy(uint32_t hint) {
+  if (hint == 1) return policy_evict_first();
+  if (hint == 2) return policy_evict_last();
+  return policy_evict_normal();
+}
+
+template <class T>
+__global__ void __launch_bounds__(T::THREADS, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_d,
+                  const KernelParams p) {
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM101_ALL)
+  constexpr int BN = T::BN;
+  constexpr int CG = T::CTA_GROUP;
+  constexpr int STAGES = T::STAGES;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* smem_store = smem + STAGES * T::STAGE_BYTES;
+  float* smem_bias = reinterpret_cast<float*>(smem_store + T::STORE_BYTES);
+  uint8_t* smem_misc = smem_store + T::STORE_BYTES + T::BIAS_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_misc);
+  // barrier layout: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_acc_full = bar_empty + STAGES * 8;
+  const uint32_t bar_acc_empty = bar_acc_full + T::ACC_BUFS * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * T::ACC_BUFS);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* last_flag = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const bool is_leader = cta_rank == 0;
+
+  const BoundedWait bw{abort_flag, p.status, p.timeout_ns};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    *last_flag = 0;
+    if ((smem_u32(smem) & 1023u) != 0) bw.give_up(ST_BAD_SMEM_ALIGN);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int b = 0; b < T::ACC_BUFS; ++b) {
+      mbar_init(bar_acc_full + b * 8, 1);
+      mbar_init(bar_acc_empty + b * 8, T::EPI_WARPS * CG);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+    if constexpr (T::EPI == EPI_SWIGLU) prefetch_tensormap(&tm_b2);
+    if constexpr (!T::TRANS_OUT) prefetch_tensormap(&tm_d);
+  }
+  if (warp == 1) {
+    tmem_alloc<CG>(smem_u32(tmem_slot), T::TMEM_COLS);
+    tmem_relinquish<CG>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) {
+    // Both CTAs' barriers must exist before either one signals the other.
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int first_unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+  const int unit_stride = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && !bw.aborted()) {
+      const uint64_t pol_a = make_policy(p.l2_hint_a);
+      const uint64_t pol_b = make_policy(p.l2_hint_b);
+      uint32_t stage = 0, phase = 0;
+      for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
+        const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY);
+          if (bw.aborted()) break;
+          const uint32_t full_local = bar_full + stage * 8;
+          const uint32_t full_bar = (CG == 2) ? map_to_cta(full_local, 0) : full_local;
+          if (is_leader) mbar_arrive_expect_tx(full_local, T::STAGE_BYTES * CG);
+          const uint32_t sa = smem_u32(smem + stage * T::STAGE_BYTES);
+          const uint32_t sb = sa + T::A_BYTES;
+          tma_load_3d<CG>(sa, &tm_a, full_bar, kb * T::BK, w.m0, w.batch, pol_a);
+          if constexpr (T::EPI == EPI_SWIGLU) {
+            // Accumulator columns [0,128) = gate, [128,256) = up.
+            if constexpr (CG == 1) {
+              tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, w.n0, 0, pol_b);
+              tma_load_3d<CG>(sb + T::B_BYTES / 2, &tm_b2, full_bar, kb * T::BK, w.n0, 0, pol_b);
+            } else {
+              tma_load_3d<CG>(sb, is_leader ? &tm_b : &tm_b2, full_bar, kb * T::BK, w.n0, 0, pol_b);
+            }
+          } else {
+            tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, w.n0 + (int)cta_rank * T::B_ROWS, w.batch,
+                            pol_b);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (bw.aborted()) break;
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0 && is_leader && !bw.aborted()) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
+        const WorkUnit w = decode_unit<T>(p, unit, 0);
+        bw.wait(bar_acc_empty + acc * 8, acc_phase ^ 1, ST_TIMEOUT_ACC_EMPTY);
+        if (bw.aborted()) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL);
+          if (bw.aborted()) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * T::STAGE_BYTES);
+          const uint64_t desc_a = umma_smem_desc_sw128(sa);
+          const uint64_t desc_b = umma_smem_desc_sw128(sa + T::A_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < T::BK / 16; ++k4) {
+            // +32 bytes (16 elements) along K inside the swizzle atom = +2 in the
+            // descriptor's 16-byte address units.
+            umma_f16<CG>(tmem_d, desc_a + 2 * k4, desc_b + 2 * k4, p.idesc,
+                         (kb > w.kb0 || k4 > 0) ? 1u : 0u);
+          }
+          if constexpr (CG == 1) {
+            umma_commit_1cta(bar_empty + stage * 8);
+          } else {
+            umma_commit_2cta(bar_empty + stage * 8, 0x3);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (bw.aborted()) break;
+        if constexpr (CG == 1) {
+          umma_commit_1cta(bar_acc_full + acc * 8);
+        } else {
+          umma_commit_2cta(bar_acc_full + acc * 8, 0x3);
+        }
+        if (++acc == T::ACC_BUFS) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;                        // TMEM lane quarter this warp may read
+    const int epi_tid = (warp - 2) * 32 + lane;    // 0..127
+    const int row_in_tile = q * 32 + lane;
+    const int is_bf16 = p.is_bf16;
+    uint8_t* my_store = smem_store + (warp - 2) * 2 * T::STORE_BUF_BYTES;
+    uint32_t store_buf = 0;
+    uint32_t acc = 0, acc_phase = 0;
+    uint32_t bias_buf = 0;
+    constexpr int CHUNKS32 = T::OUT_BN / 32 > 0 ? T::OUT_BN / 32 : 1;  // 32-column chunks
+    constexpr int CHUNK_COLS = T::OUT_BN < 32 ? T::OUT_BN : 32;
+    const uint32_t acc_empty_leader =
+        (CG == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
+
+    // No early exit in this loop: the four warps meet at named barriers, so after
+    // an abort they keep walking the units together (every wait then returns at
+    // once) and the results are garbage that the status word disowns.
+    for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
+      const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
+      const bool split_k = p.splits > 1;
+
+      if constexpr (T::EPI == EPI_BIAS && !T::TRANS_OUT) {
+        // Stage this tile's bias slice as fp32; double buffered so one barrier per
+        // tile is enough.
+        float* bdst = smem_bias + bias_buf * BN;
+        for (int c = epi_tid; c < BN; c += 128) {
+          const int col = w.n0 + c;
+          bdst[c] = (col < p.n) ? load_elem(p.bias, col, is_bf16) : 0.0f;
+        }
+        named_bar_sync(1, 128);
+      }
+
+      bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL);
+      tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+
+      // Finish one chunk of up to 32 fp32 values of this thread's row (bias, round,
+      // store).  `c32` indexes 32-column chunks of the output tile.
+      auto finish_chunk = [&](float (&v)[32], int c32) {
+        if constexpr (T::TRANS_OUT) {
+          // Kernel rows are output columns: out[batch][col][row].
+          const int row = w.m0 + row_in_tile;
+          float bias_v = 0.0f;
+          if constexpr (T::EPI == EPI_BIAS) {
+            if (row < p.m) bias_v = load_elem(p.bias, row, is_bf16);
+          }
+          if (row < p.m) {
+            uint8_t* base = reinterpret_cast<uint8_t*>(p.out) + 2 * (w.batch * p.out_batch_stride);
+#pragma unroll
+            for (int j = 0; j < CHUNK_COLS; ++j) {
+              const int col = w.n0 + c32 * 32 + j;
+              if (col < p.n) store_elem(base, col * p.out_ld + row, v[j] + bias_v, is_bf16);
+            }
+          }
+        } else {
+          if constexpr (T::EPI == EPI_BIAS) {
+            const float4* b4 = reinterpret_cast<const float4*>(smem_bias + bias_buf * BN + c32 * 32);
+#pragma unroll
+            for (int j = 0; j < CHUNK_COLS / 4; ++j) {
+              const float4 b = b4[j];
+              v[4 * j + 0] += b.x;
+              v[4 * j + 1] += b.y;
+              v[4 * j + 2] += b.z;
+              v[4 * j + 3] += b.w;
+            }
+          }
+          // Two 32-column chunks fill one 64-column (128-byte) store row.
+          const int half = c32 & 1;
+          uint8_t* buf = my_store + store_buf * T::STORE_BUF_BYTES;
+          if (half == 0) {
+            // The bulk store issued from this buffer two stores ago must have read it.
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < CHUNK_COLS / 8; ++j) {
+            uint4 pk;
+            pk.x = pack2(v[8 * j + 0], v[8 * j + 1], is_bf16);
+            pk.y = pack2(v[8 * j + 2], v[8 * j + 3], is_bf16);
+            pk.z = pack2(v[8 * j + 4], v[8 * j + 5], is_bf16);
+            pk.w = pack2(v[8 * j + 6], v[8 * j + 7], is_bf16);
+            const int chunk16 = half * 4 + j;  // 16-byte chunk within the 128-byte row
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk16 ^ (lane & 7)) << 4)) = pk;
+          }
+          const bool last_half = (half == 1) || (c32 == CHUNKS32 - 1);
+          if (last_half) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tm_d, smem_u32(buf), w.n0 + (c32 >> 1) * 64, w.m0 + q * 32, w.batch);
+              tma_store_commit();
+            }
+            store_buf ^= 1;
+          }
+        }
+      };
+
+      const bool rows_live = (w.m0 + q * 32) < p.m;
+
+      if (!split_k) {
+#pragma unroll 1
+        for (int c32 = 0; c32 < CHUNKS32; ++c32) {
+          const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
+          float v[32];
+          if constexpr (T::EPI == EPI_SWIGLU) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32(t_acc + c32 * 32, g);
+            tmem_ld_32x32(t_acc + T::OUT_BN + c32 * 32, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+          } else if constexpr (CHUNK_COLS == 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_acc + c32 * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          } else {
+            uint32_t r[16];
+            tmem_ld_32x16(t_acc, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+          }
+          if (c32 == CHUNKS32 - 1) {
+            // Whole accumulator is in registers: hand the TMEM buffer back.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CG == 2) {
+                mbar_arrive_cluster(acc_empty_leader + acc * 8);
+              } else {
+                mbar_arrive(bar_acc_empty + acc * 8);
+              }
+            }
+          }
+          // The pairing of 32-column halves into one 64-column store needs both
+          // halves handled alike, so liveness is decided per 64 columns.
+          const bool live64 = rows_live && (w.n0 + (c32 >> 1) * 64) < p.n;
+          if (T::TRANS_OUT ? live : live64) finish_chunk(v, c32);
+        }
+      } else {
+        // ---- split-K: park the fp32 partial, last arriver of the tile reduces.
+        // Slab layout: float4 index (c4, row) -> c4 * 128 + row, so a warp's
+        // 16-byte accesses are contiguous.
+        if constexpr (T::EPI != EPI_SWIGLU) {
+          float4* slab = reinterpret_cast<float4*>(p.ws) +
+                         (static_cast<size_t>(w.row_tile) * p.splits + w.split) * (32 * BN);
+#pragma unroll 1
+          for (int c32 = 0; c32 < CHUNKS32; ++c32) {
+            if constexpr (CHUNK_COLS == 32) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_acc + c32 * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                slab[(c32 * 8 + j) * 128 + row_in_tile] =
+                    make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              }
+            } else {
+              uint32_t r[16];
+              tmem_ld_32x16(t_acc, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                slab[j * 128 + row_in_tile] =
+                    make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CG == 2) {
+              mbar_arrive_cluster(acc_empty_leader + acc * 8);
+            } else {
+              mbar_arrive(bar_acc_empty + acc * 8);
+            }
+          }
+          __threadfence();
+          named_bar_sync(2, 128);
+          if (epi_tid == 0) {
+            const unsigned old = atomicAdd(p.counters + w.row_tile, 1u);
+            const bool last = (old == static_cast<unsigned>(p.splits - 1));
+            if (last) p.counters[w.row_tile] = 0;  // leave the counter clean for the next launch
+            *last_flag = last ? 1u : 0u;
+          }
+          named_bar_sync(2, 128);
+          const bool last = *last_flag != 0;
+          if (last) {
+            __threadfence();
+            const float4* tile_slabs = reinterpret_cast<const float4*>(p.ws) +
+                                       static_cast<size_t>(w.row_tile) * p.splits * (32 * BN);
+#pragma unroll 1
+            for (int c32 = 0; c32 < CHUNKS32; ++c32) {
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+              for (int s = 0; s < p.splits; ++s) {
+                const float4* sl = tile_slabs + static_cast<size_t>(s) * (32 * BN);
+#pragma unroll
+                for (int j = 0; j < CHUNK_COLS / 4; ++j) {
+                  const float4 x = __ldcg(sl + (c32 * 8 + j) * 128 + row_in_tile);
+                  v[4 * j + 0] += x.x;
+                  v[4 * j + 1] += x.y;
+                  v[4 * j + 2] += x.z;
+                  v[4 * j + 3] += x.w;
+                }
+              }
+              const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
+              const bool live64 = rows_live && (w.n0 + (c32 >> 1) * 64) < p.n;
+              if (T::TRANS_OUT ? live : live64) finish_chunk(v, c32);
+            }
+          }
+          // All four warps must have read last_flag before the next unit rewrites it.
+          named_bar_sync(2, 128);
+        }
+      }
+
+      if constexpr (T::EPI == EPI_BIAS && !T::TRANS_OUT) bias_buf ^= 1;
+      if (++acc == T::ACC_BUFS) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+    if constexpr (!T::TRANS_OUT) {
+      // Shared memory must outlive the bulk stores that read it.
+      if (lane == 0) tma_store_wait_all<0>();
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (bw.aborted()) {
+    // Give copies and MMAs that are still in flight time to land before shared
+    // memory and TMEM are released.
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) {
+    // The leader's MMAs write the peer's TMEM and both CTAs' barriers: neither
+    // CTA may free TMEM or exit before both are done.
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<CG>(tmem_base, T::TMEM_COLS);
+  }
+#endif
+}
+
+}  // namespace ayla_b200

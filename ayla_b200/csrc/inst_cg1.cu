@@ -1,0 +1,13 @@
+// Row-major-output variants, one CTA per 128-row tile.
+#include "kernel_registry.h"
+
+namespace ayla_b200 {
+void append_variants_cg1(KernelEntry* out, int* count) {
+  out[(*count)++] = make_entry<64, 1, EPI_PLAIN, false>();
+  out[(*count)++] = make_entry<128, 1, EPI_PLAIN, false>();
+  out[(*count)++] = make_entry<256, 1, EPI_PLAIN, false>();
+  out[(*count)++] = make_entry<64, 1, EPI_BIAS, false>();
+  out[(*count)++] = make_entry<128, 1, EPI_BIAS, false>();
+  out[(*count)++] = make_entry<256, 1, EPI_BIAS, false>();
+}
+}  // namespace ayla_b200

@@ -1,0 +1,76 @@
+// Table of compiled kernel variants shared between the instantiation units and
+// the C ABI.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "gemm_sm100.cuh"
+
+namespace ayla_b200 {
+
+struct LaunchArgs {
+  CUtensorMap tm_a, tm_b, tm_b2, tm_d;
+  KernelParams p;
+  int grid;
+  cudaStream_t stream;
+};
+
+struct KernelEntry {
+  int tile_n, cta_group, epilogue, transposed_out, stages, smem_bytes;
+  const void* func;
+  cudaError_t (*launch)(const LaunchArgs&);
+};
+
+constexpr int kMaxSmem = 232448;
+
+template <int BN, int CG, int EPI, bool TR>
+constexpr int max_stages() {
+  using T1 = GemmTraits<BN, CG, EPI, TR, 1>;
+  const int fixed = T1::STORE_BYTES + T1::BIAS_BYTES + T1::MISC_BYTES;
+  const int s = (kMaxSmem - fixed) / T1::STAGE_BYTES;
+  return s > 12 ? 12 : s;
+}
+
+template <class T>
+cudaError_t launch_variant(const LaunchArgs& a) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(a.grid), 1, 1);
+  cfg.blockDim = dim3(T::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[1];
+  cfg.numAttrs = 0;
+  if (T::CTA_GROUP == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<T>, a.tm_a, a.tm_b, a.tm_b2, a.tm_d, a.p);
+}
+
+template <int BN, int CG, int EPI, bool TR>
+KernelEntry make_entry() {
+  using T = GemmTraits<BN, CG, EPI, TR, max_stages<BN, CG, EPI, TR>()>;
+  KernelEntry e;
+  e.tile_n = BN;
+  e.cta_group = CG;
+  e.epilogue = EPI;
+  e.transposed_out = TR ? 1 : 0;
+  e.stages = T::STAGES;
+  e.smem_bytes = T::SMEM_BYTES;
+  e.func = reinterpret_cast<const void*>(&gemm_sm100_kernel<T>);
+  e.launch = &launch_variant<T>;
+  return e;
+}
+
+// Each instantiation unit contributes its variants.
+void append_variants_cg1(KernelEntry* out, int* count);
+void append_variants_cg2(KernelEntry* out, int* count);
+void append_variants_trans(KernelEntry* out, int* count);
+void append_variants_swiglu(KernelEntry* out, int* count);
+
+}  // namespace ayla_b200

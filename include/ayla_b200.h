@@ -1,0 +1,142 @@
+/*
+ * ayla_b200 -- C ABI of the sm_100a (B200) GEMM backend.
+ *
+ * Every entry point is plain C: raw device pointers, sizes, an opaque stream
+ * handle.  The library never allocates or frees device memory and never
+ * synchronises: a call enqueues its kernel on the given stream and returns.
+ * All functions return 0 on success or one of the AYLA_B200_E_* codes;
+ * ayla_b200_last_error() then holds a thread-local message.
+ *
+ * Operand convention (same as the reference's ops, ayla/gemm_jit.py:267-307,
+ * :396-411): all tensors are contiguous row-major 16-bit floats,
+ *     mm     out[M,N]     = a[M,K]   @ bt[N,K]^T
+ *     addmm  out[M,N]     = bias[N] + a[M,K] @ bt[N,K]^T      (bias added in fp32,
+ *                                                             before the one rounding)
+ *     bmm    out[B,M,N]   = a[B,M,K] @ bt[B,N,K]^T            (per batch)
+ * with fp32 accumulation and a single round-to-nearest-even to the output type
+ * (ayla/passes/lower_to_ptx_template.py:134-149).
+ */
+#ifndef AYLA_B200_H_
+#define AYLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define AYLA_B200_API __attribute__((visibility("default")))
+#else
+#define AYLA_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AYLA_B200_OK 0
+#define AYLA_B200_E_INVALID 1     /* bad argument (null pointer, non-positive extent, ...) */
+#define AYLA_B200_E_UNSUPPORTED 2 /* shape/alignment/config outside what the kernels cover */
+#define AYLA_B200_E_WORKSPACE 3   /* workspace missing or too small for the chosen config */
+#define AYLA_B200_E_CUDA 4        /* a CUDA runtime/driver call failed */
+#define AYLA_B200_E_NOT_INIT 5    /* ayla_b200_init() has not succeeded on this device */
+
+#define AYLA_B200_OP_MM 0
+#define AYLA_B200_OP_ADDMM 1
+#define AYLA_B200_OP_BMM 2
+
+#define AYLA_B200_F16 0
+#define AYLA_B200_BF16 1
+
+/*
+ * One kernel schedule.  It is the sm_100a counterpart of the reference's
+ * schedule dictionaries (keys of ayla/gemm_collection/gemm.py:179-198 as stored
+ * in ayla/gemm_schedule_table.py:14): tile_n ~ output_n_tile, stages ~
+ * operand_stages, grid_ctas ~ output_cta_count, group_m ~ the raster keys
+ * (swap_output_grid_axes / output_tile_fast_axis), l2_hint_* ~
+ * {lhs,rhs}_l2_cache_hint, cta_group ~ cluster_m_ctas.  The row tile is fixed
+ * at 128 per CTA (256 per CTA pair).
+ */
+typedef struct ayla_b200_config {
+  int32_t tile_n;    /* accumulator columns per tile: 16,32,64,128,256 (16/32 only with swap_ab) */
+  int32_t cta_group; /* 1, or 2 = two CTAs share one 256-row tile */
+  int32_t swap_ab;   /* 1 = compute out^T = bt @ a^T (rows of bt fill the 128-row tile); small M */
+  int32_t split_k;   /* >= 1; > 1 needs a workspace */
+  int32_t group_m;   /* raster: row tiles per group, >= 1 */
+  int32_t grid_ctas; /* persistent grid size, 0 = one CTA per SM (capped by the work) */
+  int32_t l2_hint_a; /* 0 normal, 1 evict_first, 2 evict_last; a/bt as passed by the caller */
+  int32_t l2_hint_b;
+} ayla_b200_config;
+
+/*
+ * Per-device set-up: opts every kernel into its shared-memory size and resolves
+ * the driver's tensor-map encoder.  Call once per device before the first
+ * launch and outside CUDA-graph capture.  Replaces the lazy module load of the
+ * reference's launcher (ayla/ptx_runtime.py:358-369, :53-73).
+ */
+AYLA_B200_API int ayla_b200_init(int device);
+
+/*
+ * out = [bias +] a @ bt^T on `stream` (a cudaStream_t).  Replaces the kernel
+ * launch behind gemm_op (ayla/gemm_jit.py:339-393 -> ayla/ptx_runtime.py:379-391,
+ * :237-282).  `bias` is read only for AYLA_B200_OP_ADDMM; `batch` must be 1
+ * unless op is AYLA_B200_OP_BMM.  Requirements: n % 8 == 0 and k % 8 == 0 (16-byte
+ * row pitch for TMA), all pointers 16-byte aligned.  cfg == NULL picks a schedule
+ * with ayla_b200_default_config.  `workspace` is needed only when the schedule has
+ * split_k > 1; it must hold ayla_b200_workspace_bytes(...) bytes, the first
+ * ayla_b200_workspace_counter_bytes(...) of them zero before the first use (the
+ * kernel leaves them zero).  `status`, if non-NULL, is a device uint32 the kernel
+ * sets to a non-zero code when one of its bounded waits gives up; zero it first.
+ */
+AYLA_B200_API int ayla_b200_gemm(int op, int dtype, const void* bias, const void* a, const void* bt, void* out,
+                   int64_t batch, int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg,
+                   void* workspace, size_t workspace_bytes, uint32_t* status, void* stream);
+
+/*
+ * out[M,N] = silu(x[M,K] @ w_gate[N,K]^T) * (x @ w_up[N,K]^T), both products kept
+ * in fp32 until one final rounding.  One kernel, one pass over x; the
+ * intermediates never reach HBM.  New op; its precedent is the reference's fused
+ * matmul+sigmoid op (ayla/gemm_collection/auto_matmul_4096_wgmma256_wg_sigmoid.py:22-142)
+ * and its silu/mul lowerings (ayla/passes/lower_to_ptx_template.py:296-315, :62-81).
+ * Only cfg->cta_group, group_m, grid_ctas and the L2 hints are used.
+ */
+AYLA_B200_API int ayla_b200_swiglu(int dtype, const void* x, const void* w_gate, const void* w_up, void* out,
+                     int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg, uint32_t* status,
+                     void* stream);
+
+/*
+ * The schedule ayla_b200_gemm uses when cfg == NULL.  Counterpart of
+ * select_gemm_schedule's fallback (ayla/gemm_jit.py:225-264).
+ */
+AYLA_B200_API int ayla_b200_default_config(int op, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                             ayla_b200_config* cfg_out);
+
+/*
+ * 0 if `cfg` can run the given problem, else an error code (message in
+ * ayla_b200_last_error).  Counterpart of _legal (ayla/gemm_jit.py:115-138).
+ */
+AYLA_B200_API int ayla_b200_config_valid(const ayla_b200_config* cfg, int op, int dtype, int64_t batch, int64_t m,
+                           int64_t n, int64_t k);
+
+/* Bytes of workspace `cfg` needs for the problem (0 when split_k == 1). */
+AYLA_B200_API size_t ayla_b200_workspace_bytes(const ayla_b200_config* cfg, int op, int64_t batch, int64_t m,
+                                 int64_t n, int64_t k);
+
+/* Leading bytes of that workspace that must be zero before the first launch. */
+AYLA_B200_API size_t ayla_b200_workspace_counter_bytes(const ayla_b200_config* cfg, int op, int64_t batch,
+                                         int64_t m, int64_t n, int64_t k);
+
+/* Number of compiled kernel variants, and a description of variant i. */
+AYLA_B200_API int ayla_b200_kernel_count(void);
+AYLA_B200_API int ayla_b200_kernel_info(int i, int32_t* tile_n, int32_t* cta_group, int32_t* epilogue,
+                          int32_t* transposed_out, int32_t* stages, int32_t* smem_bytes);
+
+/* Bound, in milliseconds, on every device-side wait (default 2000). */
+AYLA_B200_API void ayla_b200_set_wait_timeout_ms(int64_t ms);
+
+AYLA_B200_API const char* ayla_b200_last_error(void);
+AYLA_B200_API const char* ayla_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* AYLA_B200_H_ */
