@@ -1,0 +1,269 @@
+"""mm, addmm and bmm ops backed by the prebuilt sm_100a kernels.
+
+Drop-in for the reference's JIT GEMM front end (ayla/gemm_jit.py): the same
+names, signatures and return types --
+
+    op = gemm_op("mm", "bfloat16")      # op(a, bt, out): out = a @ bt.T
+    op(a, bt, out)
+
+``gemm_op(operation, dtype)`` returns the cached ``torch.ops.ayla.jit_{op}_{f16|bf16}``
+overload taking ``(a, bt, out)``, ``(bias, a, bt, out)`` or the batched
+``(a[B,M,K], bt[B,N,K], out[B,M,N])`` (ayla/gemm_jit.py:396-411);
+``measured_gemm_configs`` lists the schedules measured on exactly this shape and
+``select_gemm_schedule`` picks the one a launch will use (ayla/gemm_jit.py:168-222).
+A schedule here is a tile width / CTA pairing / split-K / raster choice for the
+tcgen05 kernel rather than a Hopper pass recipe, and "compiling" a shape only
+selects one: the kernels are already built into ``libayla_b200.so``.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass
+from functools import cache
+
+import torch
+
+from . import _lib
+from .gemm_schedule_table import CONFIGS, SCHEDULES
+from .jit_compiler import OpTemplate, ShapeSpecializingJITCompiler
+from .torch_custom_call import DEFAULT_NAMESPACE, OperandKind, TensorSpec
+
+_SHORT_DTYPES = {"float16": "f16", "bfloat16": "bf16"}
+_TORCH_DTYPES = {"float16": torch.float16, "bfloat16": torch.bfloat16}
+_OPERATIONS = ("mm", "addmm", "bmm")
+
+# Table entries omit default fields.
+_DEFAULTS: dict[str, object] = {
+    "tile_n": 256,
+    "cta_group": 1,
+    "swap_ab": 0,
+    "split_k": 1,
+    "group_m": 8,
+    "grid_ctas": 0,
+    "l2_hint_a": 0,
+    "l2_hint_b": 0,
+}
+
+# A measured schedule is transferred to another shape only when the shapes are
+# this close in summed |log2| of (batch, m, n, k); beyond that the shape-aware
+# default of the library is the better guess.
+_MAX_TRANSFER_DISTANCE = 2.0
+
+
+@dataclass(frozen=True)
+class GemmScheduleSeed:
+    captured_config: dict[str, object]
+    builder_config: dict[str, object] | None
+    adaptations: tuple[str, ...]
+    source_shape: tuple[int, int, int] | None
+    source_percentage_of_torch: float | None = None
+    post_builder_passes: tuple[str, ...] = ()
+
+
+def _builder_config(captured: dict[str, object]) -> dict[str, object]:
+    """The fields the launcher passes to the library (``struct ayla_b200_config``)."""
+    return {key: int(captured[key]) for key in _lib.Config.FIELDS}  # type: ignore[arg-type]
+
+
+def _shape_supported(m: int, n: int, k: int, batch: int) -> bool:
+    # 16-byte row pitch for TMA: n and k in multiples of 8 elements.  (The
+    # reference needs k % 64 == 0, ayla/gemm_jit.py:134, :234; K tails are
+    # zero-filled by TMA here, so multiples of 8 suffice.)
+    return min(batch, m, n, k) > 0 and n % 8 == 0 and k % 8 == 0
+
+
+def _legal(config: dict[str, object], operation: str, dtype: str, m: int, n: int, k: int,
+           batch: int) -> bool:
+    cfg = _lib.Config.from_dict(config)
+    return _lib.config_valid(cfg, operation, dtype, batch, m, n, k)
+
+
+def _seed(captured: dict[str, object], operation: str, dtype: str, m: int, n: int, k: int,
+          batch: int, source: tuple[int, int, int, int], exact: bool) -> GemmScheduleSeed | None:
+    if not _shape_supported(m, n, k, batch):
+        return None
+    if not _legal(captured, operation, dtype, m, n, k, batch):
+        return None
+    percentage = captured.get("percentage_of_torch")
+    return GemmScheduleSeed(
+        captured,
+        _builder_config(captured),
+        () if exact else (f"nearest measured shape {source}",),
+        source[1:],
+        float(percentage) if isinstance(percentage, (int, float)) else None,
+    )
+
+
+def measured_gemm_configs(operation: str, dtype: str, m: int, n: int, k: int,
+                          batch: int = 1) -> tuple[dict[str, object], ...]:
+    """All schedules measured on exactly this shape, winner first, as fresh copies."""
+    indices = SCHEDULES.get((operation, dtype), {}).get((batch, m, n, k), ())
+    return tuple({**_DEFAULTS, **CONFIGS[index]} for index in indices)
+
+
+def select_gemm_schedule(operation: str, dtype: str, m: int, n: int, k: int,
+                         batch: int = 1) -> GemmScheduleSeed | None:
+    """The schedule a launch of this shape uses, or ``None`` if the shape is unsupported.
+
+    An exact table hit has empty ``adaptations``; a schedule transferred from a
+    nearby measured shape names that shape; otherwise the library's shape-aware
+    default is returned with ``source_shape`` ``None``.
+    """
+    if min(batch, m, n, k) <= 0 or operation not in _OPERATIONS:
+        return None
+    table = SCHEDULES.get((operation, dtype), {})
+    if not table:
+        return None
+    if not _shape_supported(m, n, k, batch):
+        return None
+    query = (batch, m, n, k)
+
+    def distance(shape: tuple[int, int, int, int]) -> float:
+        return sum(abs(math.log2(a) - math.log2(b)) for a, b in zip(shape, query, strict=True))
+
+    for shape in sorted(table, key=distance):
+        if distance(shape) > _MAX_TRANSFER_DISTANCE:
+            break
+        for index in table[shape]:
+            seed = _seed({**_DEFAULTS, **CONFIGS[index]}, operation, dtype, m, n, k, batch, shape,
+                         exact=shape == query)
+            if seed is not None:
+                return seed
+    return _fallback_schedule(operation, dtype, m, n, k, batch)
+
+
+def _fallback_schedule(operation: str, dtype: str, m: int, n: int, k: int,
+                       batch: int = 1) -> GemmScheduleSeed | None:
+    """Unmeasured schedule from the library's heuristic (ayla_b200_default_config)."""
+    if not _shape_supported(m, n, k, batch) or dtype not in _SHORT_DTYPES:
+        return None
+    if operation not in _OPERATIONS or (operation != "bmm" and batch != 1):
+        return None
+    captured = {**_DEFAULTS, **_lib.default_config(operation, dtype, batch, m, n, k).to_dict()}
+    return GemmScheduleSeed(
+        captured,
+        _builder_config(captured),
+        ("unmeasured shape-aware default schedule",),
+        None,
+        None,
+    )
+
+
+class GemmLauncher:
+    """One specialised ``(operation, dtype, shape, device)`` launch.
+
+    Owns the split-K workspace and the device status word of its shape; both are
+    allocated here, at specialisation time, so that a launch itself allocates
+    nothing and can be captured in a CUDA graph.  Two launches of the same shape
+    that overlap on different streams would share that workspace; callers that
+    do so must serialise them.
+    """
+
+    def __init__(self, operation: str, dtype: str, batch: int, m: int, n: int, k: int,
+                 seed: GemmScheduleSeed, device: torch.device):
+        assert seed.builder_config is not None
+        self.operation, self.dtype = operation, dtype
+        self.batch, self.m, self.n, self.k = batch, m, n, k
+        self.seed = seed
+        self.device = device
+        self.config = _lib.Config.from_dict(seed.builder_config)
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        with torch.cuda.device(index):
+            _lib.init(index)
+        need = _lib.workspace_bytes(self.config, operation, batch, m, n, k)
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=device) if need else None
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._ws_ptr = self.workspace.data_ptr() if self.workspace is not None else 0
+        self._status_ptr = self.status.data_ptr()
+        self._debug = bool(os.environ.get("AYLA_B200_DEBUG"))
+
+    def __call__(self, *tensors: torch.Tensor) -> None:
+        if self.operation == "addmm":
+            bias, a, bt, out = tensors
+            bias_ptr = bias.data_ptr()
+        else:
+            a, bt, out = tensors
+            bias_ptr = 0
+        _lib.gemm(self.operation, self.dtype, bias_ptr, a.data_ptr(), bt.data_ptr(), out.data_ptr(),
+                  self.batch, self.m, self.n, self.k, self.config, self._ws_ptr,
+                  self.workspace.numel() if self.workspace is not None else 0, self._status_ptr,
+                  torch.cuda.current_stream(self.device).cuda_stream)
+        if self._debug:
+            self.check_status()
+
+    def check_status(self) -> None:
+        """Synchronise and raise if one of the kernel's bounded waits gave up."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            if self.workspace is not None:
+                self.workspace.zero_()
+            raise RuntimeError(
+                f"jit_{self.operation}: device wait timed out (code {code & 0xFF}, CTA {code >> 8})"
+            )
+
+
+def _template(operation: str, dtype: str) -> OpTemplate:
+    torch_dtype = _TORCH_DTYPES[dtype]
+    rank = 3 if operation == "bmm" else 2
+    tensor = TensorSpec(torch_dtype, (None,) * rank)
+    signature = (tensor, tensor, tensor)
+    if operation == "addmm":
+        signature = (TensorSpec(torch_dtype, (None,)), *signature)
+    return OpTemplate(f"jit_{operation}_{_SHORT_DTYPES[dtype]}", signature)
+
+
+def gemm_jit_compiler(operation: str, dtype: str) -> ShapeSpecializingJITCompiler:
+    """Per-shape dispatcher for one op: validates operands, picks the schedule once
+    per ``(device, shapes)`` and launches (ayla/gemm_jit.py:339-393)."""
+    if operation not in _OPERATIONS:
+        raise ValueError(f"unsupported GEMM operation {operation}")
+    if dtype not in _SHORT_DTYPES:
+        raise ValueError(f"unsupported GEMM dtype {dtype}")
+    template = _template(operation, dtype)
+
+    def compile_specialization(bound: OpTemplate, device: torch.device) -> GemmLauncher:
+        *bias, a, bt, out = (spec.sizes for spec in bound.signature)
+        *batch, m, k = a
+        n = bt[-2]
+        lead = tuple(batch)
+        if tuple(bt) != (*lead, n, k):
+            raise ValueError(
+                f"{bound.name}: bt must be {(*lead, n, k)} for a of shape {tuple(a)} "
+                f"(out = a @ bt.T), got {tuple(bt)}"
+            )
+        if tuple(out) != (*lead, m, n):
+            raise ValueError(f"{bound.name}: out must be {(*lead, m, n)}, got {tuple(out)}")
+        if bias and tuple(bias[0]) != (n,):
+            raise ValueError(f"{bound.name}: bias must be ({n},), got {tuple(bias[0])}")
+        schedule = select_gemm_schedule(operation, dtype, m, n, k, *batch)
+        if schedule is None:
+            raise ValueError(f"{bound.name}: no schedule for {operation} {lead}x{m}x{n}x{k}")
+        return GemmLauncher(operation, dtype, batch[0] if batch else 1, m, n, k, schedule, device)
+
+    return ShapeSpecializingJITCompiler(template, compile_specialization)
+
+
+_COMPILERS: dict[tuple[str, str, str], ShapeSpecializingJITCompiler] = {}
+
+
+@cache
+def gemm_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
+    """Torch op ``(bias?, a, bt, out) -> ()`` writing ``out = [bias +] a @ bt^T``."""
+    from .torch_custom_call import make_torch_custom_call
+
+    compiler = gemm_jit_compiler(operation, dtype)
+    _COMPILERS[(operation, dtype, namespace)] = compiler
+    inputs = 3 if operation == "addmm" else 2
+    return make_torch_custom_call(compiler, [OperandKind.R] * inputs + [OperandKind.RW],
+                                  namespace=namespace)
+
+
+def gemm_op_compiler(operation: str, dtype: str,
+                     namespace: str = DEFAULT_NAMESPACE) -> ShapeSpecializingJITCompiler:
+    """The dispatcher behind ``gemm_op(operation, dtype, namespace)`` (for its cache
+    size and the launchers' status words)."""
+    gemm_op(operation, dtype, namespace)
+    return _COMPILERS[(operation, dtype, namespace)]

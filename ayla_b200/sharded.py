@@ -1,0 +1,185 @@
+"""Multi-GPU forms of the two GEMMs that shard, one process per GPU.
+
+* ``bmm`` shards by batch: rank r owns a contiguous slice of the batch dimension of
+  a, bt and out and runs the single-GPU kernel on it.  No data-path collective.
+* a very large ``mm`` shards by N: rank r holds the row block ``bt[r*N/g:(r+1)*N/g]``
+  (= a column block of out) and all of a, computes its column block M-panel by
+  M-panel, and an NCCL all-gather of each finished panel overlaps the GEMM of the
+  next one.  A column block of a row-major matrix is not contiguous, so a panel is
+  gathered as ``[g][panel_m][N/g]`` and then copied into place.
+
+The reference is single-GPU (it has no distributed code); these follow the
+partitioning the benchmark configs ask for.  The partition arithmetic is pure
+Python so it can be tested on CPU ranks.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def partition(total: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous block ``(start, count)`` of ``total`` units owned by ``rank``;
+    the first ``total % world`` ranks take one extra unit."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    base, extra = divmod(total, world)
+    start = rank * base + min(rank, extra)
+    return start, base + (1 if rank < extra else 0)
+
+
+def column_block(n: int, world: int, rank: int) -> tuple[int, int]:
+    """Column block of an N-sharded mm.  N must split evenly into blocks whose width is
+    a multiple of 8 (16-byte rows for TMA) so every rank gathers the same amount."""
+    if n % world or (n // world) % 8:
+        raise ValueError(f"N={n} does not split into {world} equal column blocks that are multiples of 8")
+    return rank * (n // world), n // world
+
+
+@dataclass(frozen=True)
+class Panel:
+    row0: int
+    rows: int
+
+
+def m_panels(m: int, panel_rows: int) -> list[Panel]:
+    """Row panels of the N-sharded mm; the last one may be short."""
+    if panel_rows <= 0:
+        raise ValueError("panel_rows must be positive")
+    return [Panel(r, min(panel_rows, m - r)) for r in range(0, m, panel_rows)]
+
+
+def place_gathered_panel(out: torch.Tensor, gathered: torch.Tensor, panel: Panel) -> None:
+    """``gathered`` is ``[g][panel.rows][N/g]`` (rank-major, as all-gather delivers it);
+    write it to rows ``panel.row0 ..`` of the row-major ``out[M][N]``."""
+    g, rows, width = gathered.shape
+    view = out[panel.row0:panel.row0 + rows].view(rows, g, width)
+    view.copy_(gathered.permute(1, 0, 2))
+
+
+def bmm_sharded(a: torch.Tensor, bt: torch.Tensor, out: torch.Tensor, op) -> None:
+    """Run ``op(a, bt, out)`` (a ``gemm_op('bmm', ...)``) on this rank's batch slice.
+    The three tensors are this rank's local slices already."""
+    op(a, bt, out)
+
+
+class NShardedMM:
+    """``out[M, N] = a[M, K] @ bt[N, K]^T`` with bt sharded by rows across the group.
+
+    Every rank ends up with the full ``out``.  ``panel_rows`` controls the overlap
+    granularity; ``reserve_sms`` leaves that many SMs free of GEMM CTAs so the
+    all-gather kernels of NCCL can run beside the GEMM.
+    """
+
+    def __init__(self, m: int, n: int, k: int, dtype: str, device: torch.device, group=None,
+                 panel_rows: int = 4096, reserve_sms: int = 8):
+        from . import _lib
+        from .gemm_jit import _TORCH_DTYPES, select_gemm_schedule
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.m, self.n, self.k, self.dtype = m, n, k, dtype
+        self.col0, self.width = column_block(n, self.world, self.rank)
+        self.panels = m_panels(m, panel_rows)
+        self.device = device
+        _lib.init(device.index)
+        self._lib = _lib
+        torch_dtype = _TORCH_DTYPES[dtype]
+        rows = self.panels[0].rows
+        # double-buffered local panel and gather target
+        self.local = [torch.empty(rows, self.width, dtype=torch_dtype, device=device) for _ in range(2)]
+        self.gathered = [torch.empty(self.world, rows, self.width, dtype=torch_dtype, device=device)
+                         for _ in range(2)]
+        seed = select_gemm_schedule("mm", dtype, rows, self.width, k)
+        if seed is None:
+            raise ValueError(f"no schedule for panel {rows}x{self.width}x{k}")
+        cfg = dict(seed.builder_config)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        if self.world > 1 and reserve_sms > 0:
+            cfg["grid_ctas"] = (sms - reserve_sms) & ~1
+        self.cfg = _lib.Config.from_dict(cfg)
+        self.comm_stream = torch.cuda.Stream(device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def __call__(self, a: torch.Tensor, bt_shard: torch.Tensor, out: torch.Tensor) -> None:
+        lib = self._lib
+        main = torch.cuda.current_stream(self.device)
+        done_events = []
+        for i, panel in enumerate(self.panels):
+            buf = i % 2
+            if i >= 2:
+                # the gather that last read this local buffer must be finished
+                main.wait_event(done_events[i - 2])
+            local = self.local[buf][:panel.rows]
+            a_panel = a[panel.row0:panel.row0 + panel.rows]
+            lib.gemm("mm", self.dtype, 0, a_panel.data_ptr(), bt_shard.data_ptr(), local.data_ptr(), 1,
+                     panel.rows, self.width, self.k, self.cfg, 0, 0, self.status.data_ptr(), main.cuda_stream)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ready)
+                gathered = self.gathered[buf][:, :panel.rows]
+                if panel.rows == self.gathered[buf].shape[1]:
+                    dist.all_gather_into_tensor(gathered, local, group=self.group)
+                else:
+                    pieces = [torch.empty_like(local) for _ in range(self.world)]
+                    dist.all_gather(pieces, local.contiguous(), group=self.group)
+                    gathered = torch.stack(pieces)
+                place_gathered_panel(out, gathered, panel)
+                done = torch.cuda.Event()
+                done.record(self.comm_stream)
+            done_events.append(done)
+        main.wait_stream(self.comm_stream)
+
+
+def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -> dict:
+    """Timed runs of the sharded configs at this world size (device time, max over ranks)."""
+    from .gemm_jit import gemm_op
+
+    results: dict[str, object] = {}
+
+    def timed(fn, reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(reps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([start.elapsed_time(stop) / reps], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- bmm, batch 64 sharded; operands ~ the benchmark distributions
+    op = gemm_op("bmm", "bfloat16")
+    for name, (mm, nn, kk) in (("C3a", (2048, 2048, 128)), ("C3b", (2048, 128, 2048))):
+        _, count = partition(64, world, rank)
+        a = torch.randn(count, mm, kk, device=device, dtype=torch.bfloat16)
+        bt = torch.randn(count, nn, kk, device=device, dtype=torch.bfloat16)
+        out = torch.empty(count, mm, nn, device=device, dtype=torch.bfloat16)
+        ms = timed(lambda: bmm_sharded(a, bt, out, op), steps * 4)
+        flops = 2.0 * 64 * mm * nn * kk
+        results[name] = {"ms": ms, "tflops": flops / ms / 1e9, "gbs": 2.0 * 64 * (mm * kk + nn * kk + mm * nn) / ms / 1e6,
+                         "partition": f"batch 64 -> {count} per rank, no collective"}
+        del a, bt, out
+
+    # ---- mm 32768^3, N-sharded + all-gather of out
+    big = 32768
+    try:
+        runner = NShardedMM(big, big, big, "bfloat16", device)
+        a = (torch.randn(big, big, device=device, dtype=torch.float32) * big ** -0.5).bfloat16()
+        bt = (torch.randn(runner.width, big, device=device, dtype=torch.float32) * big ** -0.5).bfloat16()
+        out = torch.empty(big, big, device=device, dtype=torch.bfloat16)
+        ms = timed(lambda: runner(a, bt, out), max(1, steps // 3))
+        results["mm32768"] = {"ms": ms, "tflops": 2.0 * big ** 3 / ms / 1e9,
+                              "partition": f"N -> {runner.width} columns per rank, all-gather of out in "
+                                           f"{len(runner.panels)} M-panels"}
+    except Exception as exc:  # noqa: BLE001 - reported, not fatal for the headline line
+        results["mm32768"] = {"error": f"{type(exc).__name__}: {exc}"}
+    return results if rank == 0 else {}

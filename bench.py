@@ -1,0 +1,430 @@
+"""Benchmark of the GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--suite]
+
+Default arm: one JSON line for the headline workload, bf16 ``mm`` with
+M = N = K = 4096 (``out = a @ bt.T``), one step = one launch through the C ABI:
+
+* ``value``     TFLOP/s with operands resident in HBM (CUDA events around K launches);
+                the K launches rotate over operand sets that together exceed L2;
+* ``e2e``       the same metric through ``gemm_op`` with HOST operands: every step
+                copies a and bt from pinned host memory, launches, and copies out back;
+* ``roofline``  tensor-pipe roofline of the GEMM kernel against the measured cuBLAS
+                bf16 peak in MEASURED_PEAKS.json;
+* ``cpu_baseline`` the CPU oracle (PyTorch fp32 mm of the same operands) timed on the
+                host cores;
+* ``extra``     the fused SwiGLU config and cuBLAS (torch.mm) on the same operands.
+
+``--impl reference`` times the reference's CPU path for this workload: the reference has
+no CPU kernel of its own, its tests define the result as PyTorch's fp32 matmul
+(tests/gemm_collection/test_correctness.py:419), which is what the oracle restates.
+
+``--suite`` additionally measures every benchmark config (addmm, split-K, bmm, SwiGLU,
+the dynamic-M sweep) against cuBLAS and writes ``gpurun_out/suite.json``.
+
+With ``--gpus N`` (launched under torchrun, one rank per GPU) every rank runs the same
+workload on its own GPU (the 4096^3 GEMM does not shard usefully: replicas, weak
+scaling); ``sharded`` then reports the configs that do shard -- bmm by batch and the
+N-sharded 32768^3 mm with an NCCL all-gather of out.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+METRIC = "bf16 TFLOP/s, mm M=N=K=4096 (out = a @ bt.T)"
+WORKLOAD = "C1 mm bf16 4096x4096x4096"
+M = N = K = 4096
+FLOPS = 2.0 * M * N * K
+ALGO_BYTES = 2.0 * (M * K + N * K + M * N)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
+# summarised in profiles/ (None until measured).
+NCU_TRAFFIC_BYTES = None
+
+
+def read_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return dict(bf16=float(data["bf16_tflops"]), bf16_sustained=float(data.get("bf16_tflops_sustained", 0)),
+                    hbm=float(data["hbm_gbs"]), source="measured")
+    return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clocks, reasons, power = [], [], set(), []
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clocks.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                 parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c, p in zip(clocks, power) if p > 300.0] or clocks
+        return {
+            "sm_mhz": statistics.median(busy) if busy else None,
+            "sm_max_mhz": max(max_clocks) if max_clocks else None,
+            "power_w_max": max(power) if power else None,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+def cuda_time_ms(fn, steps: int, stream=None) -> float:
+    """Average milliseconds per call of fn(i), timed with CUDA events on the current stream."""
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(steps):
+        fn(i)
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    if world == 1:
+        return value
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def make_c1_sets(count: int, device) -> list:
+    """`count` operand sets of the C1 workload; set 0 holds the seeded benchmark inputs."""
+    from oracle import gemm_oracle as O
+
+    _, (a0, bt0) = O.make_inputs("C1", "bfloat16")
+    sets = []
+    for i in range(count):
+        if i == 0:
+            a, bt = a0.to(device), bt0.to(device)
+        else:
+            g = torch.Generator(device="cpu").manual_seed(1000 + i)
+            a = torch.randn(M, K, generator=g).bfloat16().to(device)
+            bt = torch.randn(N, K, generator=g).bfloat16().to(device)
+        sets.append((a, bt, torch.empty(M, N, dtype=torch.bfloat16, device=device)))
+    return (a0, bt0), sets
+
+
+def cpu_baseline(a0, bt0, reps: int = 3) -> dict:
+    from oracle import gemm_oracle as O
+
+    O.mm_ref32(a0[:256], bt0)  # warm the thread pool
+    best = float("inf")
+    for _ in range(reps):
+        t = time.perf_counter()
+        O.mm_ref32(a0, bt0)
+        best = min(best, time.perf_counter() - t)
+    return {
+        "value": FLOPS / best / 1e12,
+        "unit": "TFLOP/s",
+        "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": f"full workload (fp32 torch.mm of the same 4096^3 operands), best of {reps}, {best:.3f} s each",
+    }
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import gemm_oracle as O
+
+    _, (a0, bt0) = O.make_inputs("C1", "bfloat16")
+    for _ in range(max(1, min(args.warmup, 3))):
+        O.mm_ref32(a0, bt0)
+    steps = max(1, min(args.steps, 20))
+    t = time.perf_counter()
+    for _ in range(steps):
+        O.mm_ref32(a0, bt0)
+    per_step = (time.perf_counter() - t) / steps
+    value = FLOPS / per_step / 1e12
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "reference CPU path = PyTorch fp32 mm of the up-cast operands "
+                   "(the reference has no CPU kernel; its tests use this as the result definition)"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{steps} x full 4096^3 fp32 mm on CPU"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def swiglu_extra(steps: int, peaks: dict) -> dict:
+    """Fused SwiGLU x[8192,4096], W[14336,4096] (operands 537 MB > L2) vs the unfused torch path."""
+    from ayla_b200 import _lib
+
+    dev = "cuda"
+    m, n, k = 8192, 14336, 4096
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn(m, k, generator=g).bfloat16().to(dev)
+    wg = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(dev)
+    wu = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(dev)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def ours(_):
+        _lib.swiglu("bfloat16", x.data_ptr(), wg.data_ptr(), wu.data_ptr(), out.data_ptr(), m, n, k, None, 0, stream)
+
+    def unfused(_):
+        torch.nn.functional.silu(torch.mm(x, wg.t())) * torch.mm(x, wu.t())
+
+    for _ in range(3):
+        ours(0)
+        unfused(0)
+    ms = cuda_time_ms(ours, steps)
+    ms_t = cuda_time_ms(unfused, steps)
+    fl = 4.0 * m * n * k
+    return {
+        "workload": "C4 fused SwiGLU bf16 x[8192,4096] W[14336,4096]",
+        "tflops": fl / ms / 1e9, "ms": ms, "frac_of_measured_bf16_peak": fl / ms / 1e9 / peaks["bf16"],
+        "torch_unfused_tflops": fl / ms_t / 1e9, "torch_unfused_ms": ms_t,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--suite", action="store_true")
+    parser.add_argument("--no-extra", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path "
+                         "(use --impl reference for the CPU baseline)")
+
+    rank, world, local = dist_setup(args.gpus)
+    from ayla_b200 import _lib, gemm_op
+
+    device = torch.device("cuda", local if world > 1 else 0)
+    _lib.init(device.index)
+    peaks = read_peaks()
+    sets_needed = 4  # 4 x 100.7 MB of operands+output > 126 MB L2
+    (a0, bt0), sets = make_c1_sets(sets_needed, device)
+    cfg = None  # the library's schedule for this shape (same one gemm_op selects)
+    from ayla_b200.gemm_jit import select_gemm_schedule
+
+    seed = select_gemm_schedule("mm", "bfloat16", M, N, K)
+    cfg = _lib.Config.from_dict(seed.builder_config)
+    stream = torch.cuda.current_stream().cuda_stream
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def step(i):
+        a, bt, out = sets[i % len(sets)]
+        _lib.gemm("mm", "bfloat16", 0, a.data_ptr(), bt.data_ptr(), out.data_ptr(), 1, M, N, K, cfg, 0, 0,
+                  status.data_ptr(), stream)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+
+    # parity of the timed configuration before timing it
+    from oracle import gemm_oracle as O
+
+    parity = None
+    if rank == 0:
+        parity = O.compare(sets[0][2], O.mm_ref32(a0, bt0))
+        if not parity.ok:
+            raise SystemExit(f"parity failed before timing: {parity}")
+
+    sampler = ClockSampler(device.index)
+    barrier(world)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    barrier(world)
+    ms = cuda_time_ms(step, args.steps)
+    barrier(world)
+    ms = max_over_ranks(ms, world)
+    clocks = sampler.stop() if rank == 0 else None
+    if int(status.item()) != 0:
+        raise SystemExit(f"device status {int(status.item()):#x}: a bounded wait gave up")
+
+    # ---- end to end through the public op with host operands
+    op = gemm_op("mm", "bfloat16")
+    host_a = a0.pin_memory()
+    host_bt = bt0.pin_memory()
+    host_out = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    dev_a, dev_bt, dev_out = sets[0]
+
+    def e2e_step(_):
+        dev_a.copy_(host_a, non_blocking=True)
+        dev_bt.copy_(host_bt, non_blocking=True)
+        op(dev_a, dev_bt, dev_out)
+        host_out.copy_(dev_out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step(0)
+    torch.cuda.synchronize()
+    e2e_steps = max(3, min(args.steps, 20))
+    barrier(world)
+    t0 = time.perf_counter()
+    e2e_ms_events = cuda_time_ms(e2e_step, e2e_steps)
+    e2e_wall = (time.perf_counter() - t0) / e2e_steps * 1e3
+    e2e_ms = max_over_ranks(max(e2e_ms_events, e2e_wall), world)
+    barrier(world)
+
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+
+            sharded_results(args, rank, world, device)
+            dist.destroy_process_group()
+        return
+
+    value = world * FLOPS / ms / 1e9
+    achieved = FLOPS / ms / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "schedule": cfg.to_dict(),
+                   "l2": f"launches rotate over {len(sets)} operand sets, {len(sets) * ALGO_BYTES / 1e6:.0f} MB > 126 MB L2",
+                   "parallelism": "replicas" if world > 1 else "1 GPU",
+                   "inputs": "a, bt ~ N(0,1) from seed 0 (set 0); fp32 accumulate, bf16 out"},
+        "clocks": clocks,
+        "e2e": {"value": world * FLOPS / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(2 * (M * K + N * K)), "d2h_bytes_per_step": int(2 * M * N),
+                "api": "gemm_op('mm','bfloat16')(a, bt, out) with pinned host operands copied in and out every step"},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["bf16"], "traffic": NCU_TRAFFIC_BYTES,
+                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "algorithmic_bytes": ALGO_BYTES,
+                     "frac_of_nominal_2250": achieved / 2250.0},
+        "parity": {"fro_rel": parity.fro_rel, "max_over_rms": parity.max_over_rms,
+                   "over_bound": parity.over_bound, "over_bound_one_ulp": parity.over_bound_one_ulp},
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(a0, bt0)
+        if not args.no_extra:
+            a, bt, out = sets[1]
+
+            def cublas(i):
+                a, bt, out = sets[i % len(sets)]
+                torch.mm(a, bt.t(), out=out)
+
+            for i in range(3):
+                cublas(i)
+            ms_t = cuda_time_ms(cublas, args.steps)
+            line["extra"] = {"torch_mm_tflops": FLOPS / ms_t / 1e9, "torch_mm_ms": ms_t,
+                             "swiglu": swiglu_extra(max(5, args.steps // 10), peaks)}
+    else:
+        line["sharded"] = sharded_results(args, rank, world, device)
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    if args.suite and world == 1:
+        from ayla_b200.suite import run_suite
+
+        os.makedirs(ROOT / "gpurun_out", exist_ok=True)
+        rows = run_suite(peaks)
+        (ROOT / "gpurun_out" / "suite.json").write_text(json.dumps(rows, indent=1))
+    print(json.dumps(line), flush=True)
+
+
+def sharded_results(args, rank: int, world: int, device) -> dict:
+    """The configs that shard: bmm by batch (no collective) and N-sharded mm with an NCCL
+    all-gather of out.  Every rank takes part; rank 0 returns the numbers."""
+    from ayla_b200.sharded import bench_sharded
+
+    return bench_sharded(rank, world, device, steps=max(3, min(args.steps, 10)))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,322 @@
+"""Parity of the CUDA path with the CPU oracle, on a B200.
+
+Every test reaches the kernels through the C ABI (directly via ``ayla_b200._lib`` or
+through the ``torch.ops.ayla`` ops, whose CUDA implementation is a ctypes call into
+the same ABI).  Tolerance (the project's, written once in ``oracle.gemm_oracle``):
+Frobenius relative error <= 5e-3 and max elementwise error <= 2e-2 * rms(ref) against
+the CPU fp32 result rounded to the output type; elements that miss the second bound
+while being the neighbouring representable value of the reference are rounding flips
+of the last bit and are counted, not failed (``Parity.ok``).
+"""
+
+import pytest
+import torch
+
+from ayla_b200 import _lib, gemm_op, gemm_op_compiler, swiglu_op, swiglu_op_compiler
+from ayla_b200.gemm_jit import gemm_jit_compiler
+from oracle import gemm_oracle as O
+from tests.conftest import load_golden_cases
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TD = {"float16": torch.float16, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def device_state():
+    _lib.init(0)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    workspace = torch.zeros(64 << 20, dtype=torch.uint8, device=DEV)
+    return status, workspace
+
+
+def run_abi(operation, dtype, tensors, cfg, device_state, canary_rows=4):
+    """Launch through the C ABI with an explicit schedule; returns (out, status)."""
+    status, workspace = device_state
+    status.zero_()
+    dev = [t.to(DEV) for t in tensors]
+    if operation == "swiglu":
+        x, wg, wu = dev
+        m, k = x.shape
+        n = wg.shape[0]
+        store = torch.full((m + canary_rows, n), float("nan"), dtype=x.dtype, device=DEV)
+        out = store[:m]
+        _lib.swiglu(dtype, x.data_ptr(), wg.data_ptr(), wu.data_ptr(), out.data_ptr(), m, n, k,
+                    _lib.Config.from_dict(cfg) if cfg else None, status.data_ptr(),
+                    torch.cuda.current_stream().cuda_stream)
+    else:
+        bias = dev[0] if operation == "addmm" else None
+        a, bt = dev[-2:]
+        batch = a.shape[0] if operation == "bmm" else 1
+        m, k = a.shape[-2:]
+        n = bt.shape[-2]
+        rows = batch * m
+        store = torch.full((rows + canary_rows, n), float("nan"), dtype=a.dtype, device=DEV)
+        out = store[:rows].view(*a.shape[:-2], m, n)
+        _lib.gemm(operation, dtype, bias.data_ptr() if bias is not None else 0, a.data_ptr(),
+                  bt.data_ptr(), out.data_ptr(), batch, m, n, k,
+                  _lib.Config.from_dict(cfg) if cfg else None, workspace.data_ptr(), workspace.numel(),
+                  status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    # rows past the end of `out` must still hold their poison
+    assert bool(torch.isnan(store[store.shape[0] - canary_rows:]).all()), "kernel wrote past the output"
+    return out, int(status.item())
+
+
+def assert_parity(out, ref32, what=""):
+    parity = O.compare(out, ref32)
+    assert parity.ok, f"{what}: {parity}"
+    return parity
+
+
+# ------------------------------------------------------------------ golden vectors
+
+@pytest.mark.parametrize("case", load_golden_cases(), ids=repr)
+def test_ops_reproduce_golden_vectors(case):
+    operands = [t.to(DEV) for t in case.operands()]
+    want = case.expected()
+    out = torch.full(want.shape, float("nan"), dtype=case.torch_dtype, device=DEV)
+    if case.operation == "swiglu":
+        assert swiglu_op(case.dtype)(*operands, out) is None
+    else:
+        assert gemm_op(case.operation, case.dtype)(*operands, out) is None
+    torch.cuda.synchronize()
+    got = out.cpu()
+    parity = O.compare(got, want.float())
+    assert parity.ok, parity
+    # Beyond the project tolerance: a different fp32 summation order can only flip the
+    # last bit, and only on a small fraction of elements.
+    differing = int((got.view(torch.int16) != want.view(torch.int16)).sum())
+    assert differing <= max(2, got.numel() // 200), (differing, got.numel())
+    rms = float(want.float().pow(2).mean().sqrt())
+    ulp = O._ulp(want.float().abs().clamp_min(1e-2 * rms), case.torch_dtype)
+    assert bool(((got.float() - want.float()).abs() <= ulp * 1.0001).all())
+
+
+# ------------------------------------- the reference's own GPU test, op for op
+
+@pytest.mark.parametrize("operation", ["mm", "addmm", "bmm"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(96, 128, 128), (256, 256, 256)])
+def test_jit_matches_torch_and_replays_cuda_graph(operation, dtype, m, n, k):
+    """tests/test_gemm_jit.py:49-75 of the reference, same shapes and tolerances."""
+    compiler = gemm_jit_compiler(operation, str(dtype).removeprefix("torch."))
+    lead = (2,) if operation == "bmm" else ()
+    a = torch.randn((*lead, m, k), device=DEV, dtype=dtype)
+    bt = torch.randn((*lead, n, k), device=DEV, dtype=dtype)
+    out = torch.empty((*lead, m, n), device=DEV, dtype=dtype)
+    args = [a, bt, out]
+    expected = a @ bt.transpose(-1, -2)
+    if operation == "addmm":
+        bias = torch.randn(n, device=DEV, dtype=dtype)
+        args.insert(0, bias)
+        expected = torch.addmm(bias, a, bt.T)
+    compiler(*args)
+    torch.testing.assert_close(out, expected, atol=0.125, rtol=0.02)
+    assert compiler.cache_size == 1
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        compiler(*args)
+    out.zero_()
+    graph.replay()
+    torch.testing.assert_close(out, expected, atol=0.125, rtol=0.02)
+    assert compiler.cache_size == 1
+
+
+def test_capture_time_cache_miss_is_an_error():
+    compiler = gemm_jit_compiler("mm", "bfloat16")
+    a = torch.randn(64, 64, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(64, 64, device=DEV, dtype=torch.bfloat16)
+    graph = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="before capture"):
+        with torch.cuda.graph(graph):
+            compiler(a, a, out)
+
+
+# --------------------------------------------------- every kernel variant, ragged
+
+ROW_MAJOR = [(tile_n, cta_group) for tile_n in (64, 128, 256) for cta_group in (1, 2)]
+SHAPES = [
+    ("mm", 1, 128, 256, 64), ("mm", 1, 96, 128, 128), ("mm", 1, 333, 520, 200), ("mm", 1, 1, 8, 8),
+    ("addmm", 1, 300, 264, 192), ("bmm", 3, 200, 136, 128), ("mm", 1, 1024, 768, 520),
+]
+
+
+@pytest.mark.parametrize("tile_n,cta_group", ROW_MAJOR)
+@pytest.mark.parametrize("split_k", [1, 3])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_row_major_variants(tile_n, cta_group, split_k, dtype, device_state):
+    torch.manual_seed(tile_n + cta_group + split_k)
+    cfg = dict(tile_n=tile_n, cta_group=cta_group, split_k=split_k, group_m=3)
+    for operation, batch, m, n, k in SHAPES:
+        lead = (batch,) if operation == "bmm" else ()
+        a = torch.randn((*lead, m, k)).to(TD[dtype])
+        bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+        tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+        out, status = run_abi(operation, dtype, tensors, cfg, device_state)
+        assert status == 0
+        assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
+
+
+@pytest.mark.parametrize("tile_n", [16, 32, 64, 128])
+@pytest.mark.parametrize("split_k", [1, 4])
+def test_swapped_variants(tile_n, split_k, device_state):
+    torch.manual_seed(tile_n * 7 + split_k)
+    cfg = dict(tile_n=tile_n, cta_group=1, swap_ab=1, split_k=split_k, group_m=1)
+    for dtype in ("bfloat16", "float16"):
+        for operation, batch, m, n, k in (("mm", 1, 1, 256, 512), ("mm", 1, tile_n, 520, 264),
+                                          ("addmm", 1, max(1, tile_n - 3), 264, 192),
+                                          ("bmm", 3, tile_n, 136, 128), ("mm", 1, 3 * tile_n + 5, 1024, 512)):
+            lead = (batch,) if operation == "bmm" else ()
+            a = torch.randn((*lead, m, k)).to(TD[dtype])
+            bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+            tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+            out, status = run_abi(operation, dtype, tensors, cfg, device_state)
+            assert status == 0
+            assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_swiglu_variants(cta_group, dtype, device_state):
+    torch.manual_seed(cta_group)
+    for m, n, k in ((128, 128, 64), (200, 264, 192), (1, 8, 8), (1024, 2048, 1024), (520, 136, 72)):
+        x = torch.randn(m, k).to(TD[dtype])
+        wg = (torch.randn(n, k) * k ** -0.5).to(TD[dtype])
+        wu = (torch.randn(n, k) * k ** -0.5).to(TD[dtype])
+        out, status = run_abi("swiglu", dtype, (x, wg, wu), dict(cta_group=cta_group, group_m=2), device_state)
+        assert status == 0
+        assert_parity(out, O.swiglu_ref32(x, wg, wu), f"swiglu {m}x{n}x{k} cta_group={cta_group}")
+
+
+# ------------------------------------------------------------- exactness properties
+
+def test_identity_and_power_of_two_scaling_are_exact(device_state):
+    torch.manual_seed(5)
+    for dtype in ("bfloat16", "float16"):
+        td = TD[dtype]
+        a = torch.randn(300, 256).to(td)
+        eye = torch.eye(256).to(td)
+        for cfg in (dict(tile_n=256, cta_group=2), dict(tile_n=64, cta_group=1, split_k=2), None):
+            out, _ = run_abi("mm", dtype, (a, eye), cfg, device_state)
+            assert torch.equal(out.cpu(), a), cfg                      # a @ I^T == a, bit for bit
+        bt = torch.randn(264, 256).to(td)
+        base, _ = run_abi("mm", dtype, (a, bt), None, device_state)
+        scaled, _ = run_abi("mm", dtype, ((a.float() * 4).to(td), (bt.float() * 0.5).to(td)), None, device_state)
+        assert torch.equal(scaled.float().cpu(), base.float().cpu() * 2)  # exact in binary floating point
+
+
+def test_small_k_results_are_bit_exact(device_state):
+    """For K <= 128 every partial sum of 16-bit products fits fp32 exactly often enough
+    that the reference pins bit-equality with torch.mm
+    (tests/gemm_collection/test_correctness.py:216-234, :302-314); same here against the
+    CPU oracle, allowing last-bit flips on at most 0.1 % of elements."""
+    for m, n, k, seed in ((128, 256, 128, 7), (3, 256, 64, 3), (128, 256, 64, 128), (256, 256, 64, 256)):
+        g = torch.Generator().manual_seed(seed)
+        a = torch.randn(m, k, generator=g).bfloat16()
+        bt = torch.randn(n, k, generator=g).bfloat16()
+        out, _ = run_abi("mm", "bfloat16", (a, bt), None, device_state)
+        want = O.gemm_ref("mm", torch.bfloat16, a, bt)
+        differing = int((out.cpu().view(torch.int16) != want.view(torch.int16)).sum())
+        assert differing <= max(1, out.numel() // 1000), (m, n, k, differing)
+
+
+def test_repeated_launches_are_deterministic(device_state):
+    """Split-K partials are reduced in a fixed order, so results do not depend on
+    which CTA finishes last."""
+    op, tensors = O.make_inputs("C2b", "bfloat16", scale_down=4)
+    cfg = dict(tile_n=64, cta_group=1, split_k=8)
+    first, _ = run_abi(op, "bfloat16", tensors, cfg, device_state)
+    for _ in range(5):
+        again, status = run_abi(op, "bfloat16", tensors, cfg, device_state)
+        assert status == 0 and torch.equal(first, again)
+
+
+# ------------------------------------------------------------ the benchmark configs
+
+def run_op(operation, dtype, tensors):
+    dev = [t.to(DEV) for t in tensors]
+    if operation == "swiglu":
+        out = torch.empty((dev[0].shape[0], dev[1].shape[0]), dtype=dev[0].dtype, device=DEV)
+        swiglu_op(dtype)(*dev, out)
+        compiler = swiglu_op_compiler(dtype)
+    else:
+        a, bt = dev[-2:]
+        out = torch.empty((*a.shape[:-1], bt.shape[-2]), dtype=a.dtype, device=DEV)
+        gemm_op(operation, dtype)(*dev, out)
+        compiler = gemm_op_compiler(operation, dtype)
+    torch.cuda.synchronize()
+    for launcher in compiler._cache.values():
+        launcher.check_status()
+    return out
+
+
+@pytest.mark.parametrize("config,dtype", [("C1", "bfloat16"), ("C2a", "bfloat16"), ("C2a", "float16"),
+                                          ("C2b", "bfloat16"), ("C2b", "float16"), ("C3a", "bfloat16"),
+                                          ("C3b", "bfloat16"), ("C4", "bfloat16")])
+def test_benchmark_configs_full_size(config, dtype):
+    operation, tensors = O.make_inputs(config, dtype)
+    out = run_op(operation, dtype, tensors)
+    parity = assert_parity(out, O.gemm_ref32(operation, *tensors), config)
+    print(f"\n{config} {dtype}: {parity}")
+
+
+@pytest.mark.parametrize("index", range(len(O.SWEEP_M) * len(O.SWEEP_NK)))
+def test_dynamic_m_sweep(index):
+    (m, n, k), (a, bt) = O.make_sweep_inputs(index)
+    out = run_op("mm", "bfloat16", (a, bt))
+    assert_parity(out, O.mm_ref32(a, bt), f"sweep m={m} n={n} k={k}")
+
+
+def test_linearity_at_full_size():
+    """out(a1 + a2) == out(a1) + out(a2) within rounding, at the 4096^3 size, with
+    operands whose sums are exact in bf16 (small integers)."""
+    g = torch.Generator().manual_seed(9)
+    a1 = torch.randint(-3, 4, (4096, 4096), generator=g).bfloat16()
+    a2 = torch.randint(-3, 4, (4096, 4096), generator=g).bfloat16()
+    bt = torch.randint(-2, 3, (4096, 4096), generator=g).bfloat16()
+    o1 = run_op("mm", "bfloat16", (a1, bt)).float()
+    o2 = run_op("mm", "bfloat16", (a2, bt)).float()
+    o12 = run_op("mm", "bfloat16", (a1 + a2, bt)).float()
+    # integer sums below 2^24 are exact in the fp32 accumulator; only the final rounding differs
+    exact = torch.mm((a1 + a2).float(), bt.float().t()).bfloat16().float()
+    assert torch.equal(o12.cpu(), exact)
+    assert ((o1 + o2) - o12).abs().max().item() <= 2 * float(O._ulp(o12.abs().max().cpu(), torch.bfloat16))
+
+
+# ------------------------------------------------------------------ error behaviour
+
+def test_op_level_validation():
+    a = torch.randn(64, 64, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(64, 64, device=DEV, dtype=torch.bfloat16)
+    op = gemm_op("mm", "bfloat16")
+    with pytest.raises(ValueError, match="contiguous"):
+        op(a.t(), a, out)
+    with pytest.raises(ValueError, match="expected dtype"):
+        op(a.half(), a, out)
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        op(a.cpu(), a, out)
+    with pytest.raises(ValueError, match="bt must be"):
+        op(a, torch.empty(64, 32, device=DEV, dtype=torch.bfloat16), out)
+    with pytest.raises(ValueError, match="out must be"):
+        op(a, a, torch.empty(64, 32, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="no schedule"):
+        op(torch.empty(8, 12, device=DEV, dtype=torch.bfloat16), torch.empty(8, 12, device=DEV, dtype=torch.bfloat16),
+           torch.empty(8, 8, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="bias must be"):
+        gemm_op("addmm", "bfloat16")(torch.empty(32, device=DEV, dtype=torch.bfloat16), a, a, out)
+
+
+def test_abi_workspace_and_init_errors(device_state):
+    status, workspace = device_state
+    a = torch.randn(256, 1024, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(256, 256, device=DEV, dtype=torch.bfloat16)
+    cfg = _lib.Config.from_dict(dict(tile_n=64, cta_group=1, split_k=4))
+    with pytest.raises(ValueError, match="workspace"):
+        _lib.gemm("mm", "bfloat16", 0, a.data_ptr(), a.data_ptr(), out.data_ptr(), 1, 256, 256, 1024, cfg,
+                  workspace.data_ptr(), 1024, 0, torch.cuda.current_stream().cuda_stream)
+    with pytest.raises(ValueError, match="workspace"):
+        _lib.gemm("mm", "bfloat16", 0, a.data_ptr(), a.data_ptr(), out.data_ptr(), 1, 256, 256, 1024, cfg,
+                  0, 0, 0, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
