@@ -207,6 +207,12 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
   return AYLA_B200_OK;
 }
 
+// The arrival counters live in a header of fixed size at the start of the
+// workspace, whatever the shape, so one zero-initialised workspace can serve
+// launches of different shapes: data slabs never overlay a counter.
+constexpr int kMaxSplitKTiles = 16384;
+constexpr size_t kCounterBytes = static_cast<size_t>(kMaxSplitKTiles) * 4;
+
 // Fills `plan` for a validated config.  `epilogue` is one of EPI_*.
 int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t rows, int64_t cols,
               int64_t k, int sm_count, Plan* plan) {
@@ -233,6 +239,10 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
   }
   plan->total_units = static_cast<int>(units);
   plan->row_tiles = static_cast<int>(tiles * c.cta_group);
+  if (plan->splits > 1 && plan->row_tiles > kMaxSplitKTiles) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "split_k with %d output tiles (limit %d); use split_k = 1",
+                plan->row_tiles, kMaxSplitKTiles);
+  }
   plan->group_m = c.group_m;
   int grid = (c.grid_ctas > 0) ? c.grid_ctas : sm_count;
   if (c.cta_group == 2) {
@@ -249,7 +259,7 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
 
 size_t counter_bytes_for(const Plan& p) {
   if (p.splits <= 1) return 0;
-  return (static_cast<size_t>(p.row_tiles) * 4 + 255) & ~static_cast<size_t>(255);
+  return kCounterBytes;
 }
 
 size_t workspace_bytes_for(const Plan& p) {
@@ -394,6 +404,12 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
     p.counters = reinterpret_cast<unsigned*>(workspace);
     p.ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + counter_bytes_for(plan));
   }
+#ifdef AYLA_B200_TRACE
+  // Tuning builds: without split-K the workspace receives the per-CTA cycle counters.
+  if (plan.splits <= 1 && workspace != nullptr && workspace_bytes >= static_cast<size_t>(plan.grid) * 128) {
+    p.trace = reinterpret_cast<long long*>(workspace);
+  }
+#endif
   la.grid = plan.grid;
   la.stream = stream;
   const cudaError_t err = e.launch(la);

@@ -63,7 +63,26 @@ struct KernelParams {
   unsigned* counters; // split-K arrival counters, one per 128-row tile; zero between launches
   unsigned* status;   // optional device status word (may be null)
   unsigned long long timeout_ns;
+  long long* trace;   // per-CTA cycle counters, written only by AYLA_B200_TRACE builds
 };
+
+// Cycle accounting for tuning builds (-DAYLA_B200_TRACE): each role records the
+// cycles it spent inside barrier waits and its total loop time.
+#ifdef AYLA_B200_TRACE
+#define AYLA_TRACE_BEGIN long long tr_wait = 0, tr_wait2 = 0, tr_wait3 = 0, tr_tmp = 0; const long long tr_t0 = clock64();
+#define AYLA_TRACE_WAIT(acc, stmt) tr_tmp = clock64(); stmt; acc += clock64() - tr_tmp;
+#define AYLA_TRACE_END(slot)                                          \
+  if (p.trace != nullptr && (threadIdx.x & 31) == 0) {                \
+    p.trace[blockIdx.x * 16 + (slot) * 4 + 0] = tr_wait;              \
+    p.trace[blockIdx.x * 16 + (slot) * 4 + 1] = tr_wait2;             \
+    p.trace[blockIdx.x * 16 + (slot) * 4 + 2] = clock64() - tr_t0;    \
+    p.trace[blockIdx.x * 16 + (slot) * 4 + 3] = tr_wait3;             \
+  }
+#else
+#define AYLA_TRACE_BEGIN
+#define AYLA_TRACE_WAIT(acc, stmt) stmt;
+#define AYLA_TRACE_END(slot)
+#endif
 
 template <int BN_, int CTA_GROUP_, int EPI_, bool TRANS_OUT_, int STAGES_>
 struct GemmTraits {
@@ -268,89 +287,102 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int first_unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
   const int unit_stride = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
 
+  // The producer and MMA warps run their loops with all 32 lanes (addresses,
+  // coordinates and descriptors are warp-uniform, which lets the compiler keep them
+  // in uniform registers) and only one elected lane issues the asynchronous
+  // instructions.
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && !bw.aborted()) {
-      const uint64_t pol_a = make_policy(p.l2_hint_a);
-      const uint64_t pol_b = make_policy(p.l2_hint_b);
-      uint32_t stage = 0, phase = 0;
-      for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
-        const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY);
-          if (bw.aborted()) break;
-          const uint32_t full_local = bar_full + stage * 8;
-          const uint32_t full_bar = (CG == 2) ? map_to_cta(full_local, 0) : full_local;
-          if (is_leader) mbar_arrive_expect_tx(full_local, T::STAGE_BYTES * CG);
-          const uint32_t sa = smem_u32(smem + stage * T::STAGE_BYTES);
+    const bool issuer = elect_one();
+    const uint64_t pol_a = make_policy(p.l2_hint_a);
+    const uint64_t pol_b = make_policy(p.l2_hint_b);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t full_bar0 = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
+    uint32_t stage = 0, phase = 0;
+    AYLA_TRACE_BEGIN
+    for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
+      if (bw.aborted()) break;
+      const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
+      const int b_row = (T::EPI == EPI_SWIGLU) ? w.n0 : w.n0 + static_cast<int>(cta_rank) * T::B_ROWS;
+      const int b_batch = (T::EPI == EPI_SWIGLU) ? 0 : w.batch;
+      for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
+        if (issuer) {
+          const uint32_t full_bar = full_bar0 + stage * 8;
+          if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, T::STAGE_BYTES * CG);
+          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
           const uint32_t sb = sa + T::A_BYTES;
           tma_load_3d<CG>(sa, &tm_a, full_bar, kb * T::BK, w.m0, w.batch, pol_a);
-          if constexpr (T::EPI == EPI_SWIGLU) {
+          if constexpr (T::EPI == EPI_SWIGLU && CG == 1) {
             // Accumulator columns [0,128) = gate, [128,256) = up.
-            if constexpr (CG == 1) {
-              tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, w.n0, 0, pol_b);
-              tma_load_3d<CG>(sb + T::B_BYTES / 2, &tm_b2, full_bar, kb * T::BK, w.n0, 0, pol_b);
-            } else {
-              tma_load_3d<CG>(sb, is_leader ? &tm_b : &tm_b2, full_bar, kb * T::BK, w.n0, 0, pol_b);
-            }
+            tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, b_row, 0, pol_b);
+            tma_load_3d<CG>(sb + T::B_BYTES / 2, &tm_b2, full_bar, kb * T::BK, b_row, 0, pol_b);
+          } else if constexpr (T::EPI == EPI_SWIGLU) {
+            // Pair: the leader's half of the B tile is gate, the peer's half is up.
+            tma_load_3d<CG>(sb, is_leader ? &tm_b : &tm_b2, full_bar, kb * T::BK, b_row, 0, pol_b);
           } else {
-            tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, w.n0 + (int)cta_rank * T::B_ROWS, w.batch,
-                            pol_b);
-          }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
+            tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, b_row, b_batch, pol_b);
           }
         }
-        if (bw.aborted()) break;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
       }
     }
+    AYLA_TRACE_END(0)
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0 && is_leader && !bw.aborted()) {
+    if (is_leader) {
+      const bool issuer = elect_one();
+      const uint64_t desc_a0 = umma_smem_desc_sw128(smem_u32(smem));
+      const uint64_t desc_b0 = umma_smem_desc_sw128(smem_u32(smem) + T::A_BYTES);
+      const uint32_t idesc = p.idesc;
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
+      AYLA_TRACE_BEGIN
       for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
-        const WorkUnit w = decode_unit<T>(p, unit, 0);
-        bw.wait(bar_acc_empty + acc * 8, acc_phase ^ 1, ST_TIMEOUT_ACC_EMPTY);
         if (bw.aborted()) break;
+        const WorkUnit w = decode_unit<T>(p, unit, 0);
+        AYLA_TRACE_WAIT(tr_wait2, bw.wait(bar_acc_empty + acc * 8, acc_phase ^ 1, ST_TIMEOUT_ACC_EMPTY))
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL);
-          if (bw.aborted()) break;
+          AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL))
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * T::STAGE_BYTES);
-          const uint64_t desc_a = umma_smem_desc_sw128(sa);
-          const uint64_t desc_b = umma_smem_desc_sw128(sa + T::A_BYTES);
-#pragma unroll
-          for (int k4 = 0; k4 < T::BK / 16; ++k4) {
-            // +32 bytes (16 elements) along K inside the swizzle atom = +2 in the
+          if (issuer) {
+            // Stage offset and the +32 bytes per 16-element K step, both in the
             // descriptor's 16-byte address units.
-            umma_f16<CG>(tmem_d, desc_a + 2 * k4, desc_b + 2 * k4, p.idesc,
-                         (kb > w.kb0 || k4 > 0) ? 1u : 0u);
-          }
-          if constexpr (CG == 1) {
-            umma_commit_1cta(bar_empty + stage * 8);
-          } else {
-            umma_commit_2cta(bar_empty + stage * 8, 0x3);
+            const uint32_t stage_off = stage * (T::STAGE_BYTES >> 4);
+#pragma unroll
+            for (int k4 = 0; k4 < T::BK / 16; ++k4) {
+              umma_f16<CG>(tmem_d, desc_a0 + (stage_off + 2 * k4), desc_b0 + (stage_off + 2 * k4), idesc,
+                           (kb > w.kb0 || k4 > 0) ? 1u : 0u);
+            }
+            if constexpr (CG == 1) {
+              umma_commit_1cta(bar_empty + stage * 8);
+            } else {
+              umma_commit_2cta(bar_empty + stage * 8, 0x3);
+            }
+            if (kb == w.kb1 - 1) {
+              if constexpr (CG == 1) {
+                umma_commit_1cta(bar_acc_full + acc * 8);
+              } else {
+                umma_commit_2cta(bar_acc_full + acc * 8, 0x3);
+              }
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
-        }
-        if (bw.aborted()) break;
-        if constexpr (CG == 1) {
-          umma_commit_1cta(bar_acc_full + acc * 8);
-        } else {
-          umma_commit_2cta(bar_acc_full + acc * 8, 0x3);
         }
         if (++acc == T::ACC_BUFS) {
           acc = 0;
           acc_phase ^= 1;
         }
       }
+      AYLA_TRACE_END(1)
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -366,6 +398,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     constexpr int CHUNK_COLS = T::OUT_BN < 32 ? T::OUT_BN : 32;
     const uint32_t acc_empty_leader =
         (CG == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
+    AYLA_TRACE_BEGIN
 
     // No early exit in this loop: the four warps meet at named barriers, so after
     // an abort they keep walking the units together (every wait then returns at
@@ -385,7 +418,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         named_bar_sync(1, 128);
       }
 
-      bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL);
+      AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL))
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 
@@ -583,6 +616,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if constexpr (!T::TRANS_OUT) {
       // Shared memory must outlive the bulk stores that read it.
       if (lane == 0) tma_store_wait_all<0>();
+    }
+    if (warp == 2) {
+      AYLA_TRACE_END(2)
     }
   }
 

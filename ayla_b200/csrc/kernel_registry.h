@@ -29,7 +29,11 @@ constexpr int max_stages() {
   using T1 = GemmTraits<BN, CG, EPI, TR, 1>;
   const int fixed = T1::STORE_BYTES + T1::BIAS_BYTES + T1::MISC_BYTES;
   const int s = (kMaxSmem - fixed) / T1::STAGE_BYTES;
+#ifdef AYLA_B200_STAGE_CAP
+  return s > AYLA_B200_STAGE_CAP ? AYLA_B200_STAGE_CAP : s;
+#else
   return s > 12 ? 12 : s;
+#endif
 }
 
 template <class T>

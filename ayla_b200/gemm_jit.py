@@ -249,9 +249,15 @@ def gemm_jit_compiler(operation: str, dtype: str) -> ShapeSpecializingJITCompile
 _COMPILERS: dict[tuple[str, str, str], ShapeSpecializingJITCompiler] = {}
 
 
-@cache
 def gemm_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
-    """Torch op ``(bias?, a, bt, out) -> ()`` writing ``out = [bias +] a @ bt^T``."""
+    """Torch op ``(bias?, a, bt, out) -> ()`` writing ``out = [bias +] a @ bt^T``.
+
+    Cached: the same overload object is returned for the same arguments."""
+    return _gemm_op(operation, dtype, namespace)
+
+
+@cache
+def _gemm_op(operation: str, dtype: str, namespace: str) -> torch._ops.OpOverload:
     from .torch_custom_call import make_torch_custom_call
 
     compiler = gemm_jit_compiler(operation, dtype)

@@ -183,3 +183,22 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
     except Exception as exc:  # noqa: BLE001 - reported, not fatal for the headline line
         results["mm32768"] = {"error": f"{type(exc).__name__}: {exc}"}
     return results if rank == 0 else {}
+
+
+def n_sharded_mm_unoverlapped(a: torch.Tensor, bt_shard: torch.Tensor, out: torch.Tensor, gemm_fn,
+                              group=None, panel_rows: int = 4096) -> None:
+    """The same partition / panel / gather / placement sequence as ``NShardedMM`` without
+    streams: ``gemm_fn(a_panel, bt_shard, local_out)`` computes one panel of this rank's
+    column block.  Device-agnostic, so the data movement can be checked on CPU ranks."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    m, n = out.shape
+    _, width = column_block(n, world, rank)
+    if bt_shard.shape[0] != width:
+        raise ValueError(f"rank {rank}: bt shard has {bt_shard.shape[0]} rows, expected {width}")
+    for panel in m_panels(m, panel_rows):
+        local = torch.empty(panel.rows, width, dtype=out.dtype, device=out.device)
+        gemm_fn(a[panel.row0:panel.row0 + panel.rows], bt_shard, local)
+        pieces = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(pieces, local, group=group)
+        place_gathered_panel(out, torch.stack(pieces), panel)

@@ -73,9 +73,13 @@ def swiglu_compiler(dtype: str) -> ShapeSpecializingJITCompiler:
 _COMPILERS: dict[tuple[str, str], ShapeSpecializingJITCompiler] = {}
 
 
-@cache
 def swiglu_op(dtype: str = "bfloat16", namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
-    """Torch op ``(x, w_gate, w_up, out) -> ()``."""
+    """Torch op ``(x, w_gate, w_up, out) -> ()`` (cached per dtype and namespace)."""
+    return _swiglu_op(dtype, namespace)
+
+
+@cache
+def _swiglu_op(dtype: str, namespace: str) -> torch._ops.OpOverload:
     compiler = swiglu_compiler(dtype)
     _COMPILERS[(dtype, namespace)] = compiler
     return make_torch_custom_call(compiler, [OperandKind.R] * 3 + [OperandKind.RW], namespace=namespace)

@@ -120,7 +120,11 @@ AYLA_B200_API int ayla_b200_config_valid(const ayla_b200_config* cfg, int op, in
 AYLA_B200_API size_t ayla_b200_workspace_bytes(const ayla_b200_config* cfg, int op, int64_t batch, int64_t m,
                                  int64_t n, int64_t k);
 
-/* Leading bytes of that workspace that must be zero before the first launch. */
+/*
+ * Leading bytes of that workspace that must be zero before the first launch (the
+ * split-K arrival counters; 64 KiB for every shape, so a workspace zeroed once can
+ * be shared by launches of different shapes).  The kernel returns them to zero.
+ */
 AYLA_B200_API size_t ayla_b200_workspace_counter_bytes(const ayla_b200_config* cfg, int op, int64_t batch,
                                          int64_t m, int64_t n, int64_t k);
 

@@ -98,15 +98,17 @@ def test_workspace_sizing():
     none = _lib.Config.from_dict(dict(tile_n=256, cta_group=1, split_k=1))
     assert _lib.workspace_bytes(none, "mm", 1, 256, 1024, 16384) == 0
     cfg = _lib.Config.from_dict(dict(tile_n=64, cta_group=1, split_k=4))
-    # 2 row tiles x 16 column tiles, 4 splits, 128 x 64 fp32 slabs, + counters rounded to 256 B
+    # 2 row tiles x 16 column tiles, 4 splits, 128 x 64 fp32 slabs, + the fixed 64 KiB counter header
     counters = _lib.workspace_counter_bytes(cfg, "mm", 1, 256, 1024, 16384)
-    assert counters == 256
+    assert counters == 65536
     assert _lib.workspace_bytes(cfg, "mm", 1, 256, 1024, 16384) == counters + 32 * 4 * 128 * 64 * 4
     # more splits than 64-wide k blocks are clamped
     deep = _lib.Config.from_dict(dict(tile_n=64, cta_group=1, split_k=64))
-    assert _lib.workspace_bytes(deep, "mm", 1, 128, 64, 128) == 256 + 1 * 2 * 128 * 64 * 4
+    assert _lib.workspace_bytes(deep, "mm", 1, 128, 64, 128) == 65536 + 1 * 2 * 128 * 64 * 4
+    huge = _lib.Config.from_dict(dict(tile_n=64, cta_group=1, split_k=2))
+    assert not _lib.config_valid(huge, "mm", "bfloat16", 1, 128 * 200, 64 * 100, 256)  # 20000 tiles
     pair = _lib.Config.from_dict(dict(tile_n=128, cta_group=2, split_k=2))
-    assert _lib.workspace_bytes(pair, "mm", 1, 256, 128, 1024) == 256 + 2 * 2 * 128 * 128 * 4
+    assert _lib.workspace_bytes(pair, "mm", 1, 256, 128, 1024) == 65536 + 2 * 2 * 128 * 128 * 4
 
 
 def test_gemm_rejects_bad_arguments_before_touching_the_device():

@@ -1,0 +1,101 @@
+"""Partition arithmetic and the gather/placement data movement of the sharded GEMMs,
+on two CPU ranks over gloo (no GPU).  The per-rank GEMM is played by the CPU oracle."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ayla_b200 import sharded
+from oracle import gemm_oracle as O
+
+
+def test_partition_covers_everything_once():
+    for total, world in ((64, 8), (64, 4), (10, 4), (3, 8), (1, 1)):
+        blocks = [sharded.partition(total, world, r) for r in range(world)]
+        assert blocks[0][0] == 0
+        for (s0, c0), (s1, _) in zip(blocks, blocks[1:]):
+            assert s0 + c0 == s1
+        assert blocks[-1][0] + blocks[-1][1] == total
+        assert max(c for _, c in blocks) - min(c for _, c in blocks) <= 1
+    with pytest.raises(ValueError):
+        sharded.partition(8, 2, 2)
+
+
+def test_column_blocks_and_panels():
+    assert [sharded.column_block(32768, 8, r) for r in (0, 7)] == [(0, 4096), (28672, 4096)]
+    with pytest.raises(ValueError):
+        sharded.column_block(100, 8, 0)      # not divisible
+    with pytest.raises(ValueError):
+        sharded.column_block(8 * 12, 8, 0)   # blocks of 12 columns: not 16-byte rows
+    panels = sharded.m_panels(10000, 4096)
+    assert [(p.row0, p.rows) for p in panels] == [(0, 4096), (4096, 4096), (8192, 1808)]
+
+
+def test_place_gathered_panel_unpermutes():
+    out = torch.zeros(6, 8)
+    gathered = torch.arange(2 * 3 * 4, dtype=torch.float32).view(2, 3, 4)
+    sharded.place_gathered_panel(out, gathered, sharded.Panel(2, 3))
+    assert torch.equal(out[2], torch.tensor([0., 1, 2, 3, 12, 13, 14, 15]))
+    assert torch.equal(out[4], torch.tensor([8., 9, 10, 11, 20, 21, 22, 23]))
+    assert not out[:2].any() and not out[5:].any()
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)          # same operands on every rank
+        m, n, k = 200, 64 * world, 96
+        a = torch.randn(m, k, generator=g).bfloat16()
+        bt = (torch.randn(n, k, generator=g) * k ** -0.5).bfloat16()
+        full = O.gemm_ref("mm", torch.bfloat16, a, bt)
+
+        # N-sharded mm: this rank only ever sees its row block of bt
+        col0, width = sharded.column_block(n, world, rank)
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16)
+        sharded.n_sharded_mm_unoverlapped(
+            a, bt[col0:col0 + width].contiguous(), out,
+            lambda ap, bs, local: local.copy_(O.gemm_ref("mm", torch.bfloat16, ap, bs)), panel_rows=64)
+        ok_mm = torch.equal(out.view(torch.int16), full.view(torch.int16))
+
+        # batch-sharded bmm: slices are independent; gather only to compare
+        batch = 5
+        a3 = torch.randn(batch, 40, 32, generator=g).bfloat16()
+        bt3 = torch.randn(batch, 24, 32, generator=g).bfloat16()
+        start, count = sharded.partition(batch, world, rank)
+        mine = torch.empty(count, 40, 24, dtype=torch.bfloat16)
+        sharded.bmm_sharded(a3[start:start + count], bt3[start:start + count], mine,
+                            lambda x, y, o: o.copy_(O.gemm_ref("bmm", torch.bfloat16, x, y)))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (start, mine))
+        whole = torch.cat([t for _, t in sorted(gathered, key=lambda p: p[0])])
+        ok_bmm = torch.equal(whole.view(torch.int16), O.gemm_ref("bmm", torch.bfloat16, a3, bt3).view(torch.int16))
+
+        # a rank with a wrong shard is caught before any collective
+        try:
+            sharded.n_sharded_mm_unoverlapped(a, bt[: width + 8].contiguous(), out, None)
+            ok_err = False
+        except ValueError:
+            ok_err = True
+        results[rank] = (ok_mm, ok_bmm, ok_err)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_flows_on_two_gloo_ranks():
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {0: (True, True, True), 1: (True, True, True)}
