@@ -22,6 +22,7 @@ E_INVALID, E_UNSUPPORTED, E_WORKSPACE, E_CUDA, E_NOT_INIT = 1, 2, 3, 4, 5
 EXPORTS = (
     "ayla_b200_init",
     "ayla_b200_gemm",
+    "ayla_b200_gemm_static_scratch",
     "ayla_b200_swiglu",
     "ayla_b200_default_config",
     "ayla_b200_config_valid",
@@ -103,6 +104,8 @@ def load() -> ctypes.CDLL:
         lib.ayla_b200_init.restype = i32
         lib.ayla_b200_gemm.argtypes = [i32, i32, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, sz, vp, vp]
         lib.ayla_b200_gemm.restype = i32
+        lib.ayla_b200_gemm_static_scratch.argtypes = [i32, i32, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, vp]
+        lib.ayla_b200_gemm_static_scratch.restype = i32
         lib.ayla_b200_swiglu.argtypes = [i32, vp, vp, vp, vp, i64, i64, i64, cfgp, vp, vp]
         lib.ayla_b200_swiglu.restype = i32
         lib.ayla_b200_default_config.argtypes = [i32, i32, i64, i64, i64, i64, cfgp]
@@ -195,6 +198,19 @@ def gemm(op: str, dtype: str, bias_ptr: int, a_ptr: int, bt_ptr: int, out_ptr: i
         OP_CODES[op], DTYPE_CODES[dtype], bias_ptr or None, a_ptr, bt_ptr, out_ptr, batch, m, n, k,
         ctypes.byref(cfg) if cfg is not None else None, workspace_ptr or None, workspace_size,
         status_ptr or None, stream or None))
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def gemm_static_scratch(op: str, dtype: str, bias_ptr: int, a_ptr: int, bt_ptr: int, out_ptr: int,
+                        batch: int, m: int, n: int, k: int, cfg: Config | None, status_ptr: int,
+                        stream: int) -> None:
+    """``gemm`` for callers that cannot provide or allocate a workspace: split-K scratch
+    comes from the 8 MiB array built into the library (see ``include/ayla_b200.h``)."""
+    check(load().ayla_b200_gemm_static_scratch(
+        OP_CODES[op], DTYPE_CODES[dtype], bias_ptr or None, a_ptr, bt_ptr, out_ptr, batch, m, n, k,
+        ctypes.byref(cfg) if cfg is not None else None, status_ptr or None, stream or None))
 
 
 def swiglu(dtype: str, x_ptr: int, wg_ptr: int, wu_ptr: int, out_ptr: int, m: int, n: int, k: int,

@@ -419,6 +419,33 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   return AYLA_B200_OK;
 }
 
+// ----------------------------------------------------- built-in split-K scratch
+//
+// Scratch for ayla_b200_gemm_static_scratch: a fixed array in device memory that is
+// part of the loaded library image on every GPU, so that entry point never has to
+// ask anyone for memory.  In host code `g_static_scratch` is only a handle for
+// the runtime (not a device address); the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[AYLA_B200_STATIC_SCRATCH_BYTES];
+
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kMaxDevices] = {};
+
+int static_scratch_for_current_device(int device, void** out) {
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      return fail(AYLA_B200_E_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", device,
+                  cudaGetErrorString(err));
+    }
+    g_scratch_ptr[device] = ptr;
+  }
+  *out = g_scratch_ptr[device];
+  return AYLA_B200_OK;
+}
+
 }  // namespace
 }  // namespace ayla_b200
 
@@ -575,6 +602,66 @@ int ayla_b200_gemm(int op, int dtype, const void* bias, const void* a, const voi
   if (rc) return rc;
   return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, workspace,
                      workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ayla_b200_gemm_static_scratch(int op, int dtype, const void* bias, const void* a, const void* bt,
+                                  void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
+                                  const ayla_b200_config* cfg, uint32_t* status, void* stream) {
+  int rc = check_shape(op, dtype, batch, m, n, k);
+  if (rc) return rc;
+  if (a == nullptr || bt == nullptr || out == nullptr) {
+    return fail(AYLA_B200_E_INVALID, "a, bt and out must be non-null");
+  }
+  if (op == AYLA_B200_OP_ADDMM && bias == nullptr) {
+    return fail(AYLA_B200_E_INVALID, "addmm needs a bias pointer");
+  }
+  if (!aligned16(a) || !aligned16(bt) || !aligned16(out)) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "a, bt and out must be 16-byte aligned");
+  }
+  DeviceState* ds = nullptr;
+  int dev = -1;
+  rc = current_device_state(&ds, &dev);
+  if (rc) return rc;
+  ayla_b200_config c;
+  if (cfg != nullptr) {
+    c = *cfg;
+  } else {
+    default_config(batch, m, n, k, ds->sm_count, &c);
+  }
+  rc = check_config(c, false);
+  if (rc) return rc;
+  Problem pr;
+  pr.k = k;
+  pr.batch = batch;
+  pr.rows = c.swap_ab ? n : m;
+  pr.cols = c.swap_ab ? m : n;
+  pr.row_operand = c.swap_ab ? bt : a;
+  pr.col_operand = c.swap_ab ? a : bt;
+  const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
+  Plan plan;
+  rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan);
+  if (rc) return rc;
+  const size_t need = workspace_bytes_for(plan);
+  if (need > static_cast<size_t>(AYLA_B200_STATIC_SCRATCH_BYTES)) {
+    return fail(AYLA_B200_E_WORKSPACE,
+                "this schedule needs %zu bytes of split-K scratch; the built-in array holds %zu "
+                "(use ayla_b200_gemm with a caller workspace, or a smaller split_k)",
+                need, static_cast<size_t>(AYLA_B200_STATIC_SCRATCH_BYTES));
+  }
+  void* scratch = nullptr;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (need > 0) {
+    rc = static_scratch_for_current_device(dev, &scratch);
+    if (rc) return rc;
+    // The array keeps whatever the previous call left behind.  Only the arrival
+    // counters must start at zero; partial sums are fully rewritten before they are read.
+    const cudaError_t err = cudaMemsetAsync(scratch, 0, static_cast<size_t>(plan.row_tiles) * 4, s);
+    if (err != cudaSuccess) {
+      return fail(AYLA_B200_E_CUDA, "clearing the split-K counters: %s", cudaGetErrorString(err));
+    }
+  }
+  return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, scratch, need,
+                     status, s);
 }
 
 int ayla_b200_swiglu(int dtype, const void* x, const void* w_gate, const void* w_up, void* out,

@@ -91,6 +91,45 @@ AYLA_B200_API int ayla_b200_gemm(int op, int dtype, const void* bias, const void
                    void* workspace, size_t workspace_bytes, uint32_t* status, void* stream);
 
 /*
+ * Size of the scratch array built into the library for
+ * ayla_b200_gemm_static_scratch: 8 MiB of device memory on every GPU that loads
+ * the library, held until the process exits.
+ */
+#define AYLA_B200_STATIC_SCRATCH_BYTES (8u << 20)
+
+/*
+ * ayla_b200_gemm for callers that have no device memory to lend and may not
+ * allocate any.  (No counterpart in the reference, which never needs scratch:
+ * it has no split-K schedule.)
+ *
+ * Who needs it: a host that drives this library from inside another runtime's
+ * memory regime -- an inference server or framework plugin that owns a fixed
+ * pool and forbids cudaMalloc underneath it (cudaMalloc and cudaFree stall the
+ * whole device and bypass the pool's accounting), or code that only ever sees the
+ * operand pointers of one op and has nowhere to keep a workspace between calls.
+ * For them the partial sums and arrival counters of a split-K schedule live in a
+ * fixed array of AYLA_B200_STATIC_SCRATCH_BYTES inside the library image; the
+ * caller passes operands and output only.  The call allocates nothing: no
+ * cudaMalloc, no cudaFree, no allocating library routine.
+ *
+ * Same arguments and results as ayla_b200_gemm without the workspace pair.
+ * A schedule whose scratch need exceeds the array is refused with
+ * AYLA_B200_E_WORKSPACE and a message naming both sizes (schedules with
+ * split_k == 1 need none and always fit).
+ *
+ * The first call on a device that needs scratch resolves the array's device
+ * address (a one-off runtime query); make that first call outside stream
+ * capture.  All calls on a GPU share the one array and it keeps the previous
+ * call's contents: the entry point clears the arrival counters on `stream`
+ * before each launch, and two calls whose kernels can overlap on the GPU
+ * (different streams, no dependency) race on it -- serialise them.
+ */
+AYLA_B200_API int ayla_b200_gemm_static_scratch(int op, int dtype, const void* bias, const void* a,
+                                                const void* bt, void* out, int64_t batch, int64_t m,
+                                                int64_t n, int64_t k, const ayla_b200_config* cfg,
+                                                uint32_t* status, void* stream);
+
+/*
  * out[M,N] = silu(x[M,K] @ w_gate[N,K]^T) * (x @ w_up[N,K]^T), both products kept
  * in fp32 until one final rounding.  One kernel, one pass over x; the
  * intermediates never reach HBM.  New op; its precedent is the reference's fused
