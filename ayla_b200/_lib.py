@@ -48,6 +48,7 @@ class Config(ctypes.Structure):
         ("grid_ctas", ctypes.c_int32),
         ("l2_hint_a", ctypes.c_int32),
         ("l2_hint_b", ctypes.c_int32),
+        ("split_tail", ctypes.c_int32),
     ]
 
     FIELDS = tuple(name for name, _ in _fields_)
@@ -55,7 +56,7 @@ class Config(ctypes.Structure):
     @classmethod
     def from_dict(cls, values: dict) -> "Config":
         cfg = cls(tile_n=256, cta_group=1, swap_ab=0, split_k=1, group_m=8, grid_ctas=0,
-                  l2_hint_a=0, l2_hint_b=0)
+                  l2_hint_a=0, l2_hint_b=0, split_tail=0)
         for key in cls.FIELDS:
             if key in values and values[key] is not None:
                 setattr(cfg, key, int(values[key]))

@@ -147,6 +147,8 @@ struct Problem {
 struct Plan {
   const KernelEntry* kernel;
   int m_tiles, n_tiles, k_blocks, splits, kb_per_split, total_units, group_m, grid;
+  int split_from_tile;  // first k-split tile (0 = all tiles split, == tiles when none is)
+  int narrow_from_tile; // first tile done as two half-width units (== tiles when none is)
   int row_tiles;  // 128-row x tile_n tiles (split-K counters, slabs)
 };
 
@@ -184,6 +186,13 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
   }
   if (c.split_k < 1 || c.group_m < 1 || c.grid_ctas < 0) {
     return fail(AYLA_B200_E_UNSUPPORTED, "split_k and group_m must be >= 1, grid_ctas >= 0");
+  }
+  if (c.split_tail < 0 || c.split_tail > 2) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "split_tail must be 0, 1 or 2");
+  }
+  if (c.split_tail == 2 && (swiglu || c.swap_ab || c.split_k != 1 || c.tile_n < 128)) {
+    return fail(AYLA_B200_E_UNSUPPORTED,
+                "split_tail = 2 (half-width last wave) needs tile_n >= 128, split_k = 1 and no swap_ab");
   }
   if (c.l2_hint_a < 0 || c.l2_hint_a > 2 || c.l2_hint_b < 0 || c.l2_hint_b > 2) {
     return fail(AYLA_B200_E_UNSUPPORTED, "L2 hints must be 0, 1 or 2");
@@ -233,26 +242,50 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
   plan->kb_per_split = static_cast<int>(ceil_div(plan->k_blocks, splits));
   plan->splits = static_cast<int>(ceil_div(plan->k_blocks, plan->kb_per_split));
   const int64_t tiles = static_cast<int64_t>(batch) * plan->m_tiles * plan->n_tiles;
-  const int64_t units = tiles * plan->splits;
-  if (units > 0x7FFFFFFF || tiles * c.cta_group > 0x7FFFFFFF) {
-    return fail(AYLA_B200_E_UNSUPPORTED, "too many tiles (%lld)", (long long)units);
+  if (tiles * c.cta_group > 0x7FFFFFFF) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "too many tiles (%lld)", (long long)tiles);
+  }
+  int grid = (c.grid_ctas > 0) ? c.grid_ctas : sm_count;
+  if (c.cta_group == 2) {
+    grid &= ~1;
+    if (grid < 2) grid = 2;
+  } else if (grid < 1) {
+    grid = 1;
+  }
+  // Tiles processed at the same time by the persistent grid.
+  const int64_t wave = grid / c.cta_group;
+  int64_t split_from = 0;
+  if (plan->splits <= 1) {
+    split_from = tiles;
+  } else if (c.split_tail) {
+    // Only the tiles of the last, partial wave are k-split; with less than one wave of
+    // tiles that is all of them, with a whole number of waves none.
+    split_from = (tiles / wave) * wave;
+    if (split_from == tiles) {
+      plan->splits = 1;
+      plan->kb_per_split = plan->k_blocks;
+    }
+  }
+  plan->split_from_tile = static_cast<int>(split_from);
+  int64_t narrow_from = tiles;
+  if (c.split_tail == 2 && tiles > wave && tiles % wave != 0) {
+    // The tiles of the last, partial wave are done as two half-width units each.
+    narrow_from = (tiles / wave) * wave;
+  }
+  // INT_MAX = no narrow units (unit indices of k-split tiles run past `tiles`).
+  plan->narrow_from_tile = (narrow_from == tiles) ? 0x7FFFFFFF : static_cast<int>(narrow_from);
+  const int64_t units = split_from + (tiles - split_from) * plan->splits + (tiles - narrow_from);
+  if (units > 0x7FFFFFFF) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "too many work units (%lld)", (long long)units);
   }
   plan->total_units = static_cast<int>(units);
-  plan->row_tiles = static_cast<int>(tiles * c.cta_group);
+  plan->row_tiles = static_cast<int>((tiles - split_from) * c.cta_group);
   if (plan->splits > 1 && plan->row_tiles > kMaxSplitKTiles) {
     return fail(AYLA_B200_E_UNSUPPORTED, "split_k with %d output tiles (limit %d); use split_k = 1",
                 plan->row_tiles, kMaxSplitKTiles);
   }
   plan->group_m = c.group_m;
-  int grid = (c.grid_ctas > 0) ? c.grid_ctas : sm_count;
-  if (c.cta_group == 2) {
-    grid &= ~1;
-    if (grid < 2) grid = 2;
-    if (static_cast<int64_t>(grid / 2) > units) grid = static_cast<int>(2 * units);
-  } else {
-    if (grid < 1) grid = 1;
-    if (static_cast<int64_t>(grid) > units) grid = static_cast<int>(units);
-  }
+  if (wave > units) grid = static_cast<int>(units * c.cta_group);
   plan->grid = grid;
   return AYLA_B200_OK;
 }
@@ -333,9 +366,18 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
     }
   }
   c->tile_n = tile_n;
-  const int64_t tiles = batch * ceil_div(m, 128) * ceil_div(n, tile_n);
-  if (m >= 256 && tiles >= 2 * static_cast<int64_t>(sm_count)) c->cta_group = 2;
-  if (tiles * 2 <= sm_count && k_blocks >= 16) {
+  int64_t tiles = batch * ceil_div(m, 128) * ceil_div(n, tile_n);
+  if (m >= 256 && tiles >= static_cast<int64_t>(sm_count)) {
+    c->cta_group = 2;
+    tiles = batch * ceil_div(m, 256) * ceil_div(n, tile_n);
+  }
+  const int64_t wave = sm_count / c->cta_group;
+  const int64_t rest = tiles % wave;
+  if (tiles > wave && rest != 0 && rest * 2 <= wave && tile_n >= 128) {
+    // More than one wave with a thin last wave: do those tiles as half-width units so
+    // the last wave keeps every SM busy.
+    c->split_tail = 2;
+  } else if (tiles * 2 <= sm_count && k_blocks >= 16) {
     int64_t s = sm_count / tiles;
     const int64_t max_s = k_blocks / 8;
     if (s > max_s) s = max_s;
@@ -379,6 +421,9 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.k_blocks = plan.k_blocks;
   p.splits = plan.splits;
   p.kb_per_split = plan.kb_per_split;
+  p.split_from_tile = plan.split_from_tile;
+  p.narrow_from_tile = plan.narrow_from_tile;
+  p.idesc_narrow = make_idesc(is_bf16, 128 * e.cta_group, e.tile_n / 2);
   p.total_units = plan.total_units;
   p.group_m = plan.group_m;
   p.is_bf16 = is_bf16;

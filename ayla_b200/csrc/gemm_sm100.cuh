@@ -47,8 +47,11 @@ struct KernelParams {
   int m_tiles;        // tiles of 128*CTA_GROUP rows
   int n_tiles;        // tiles of the output tile width
   int k_blocks;       // ceil(k / 64)
-  int splits;         // k-splits per tile (1 = none)
+  int splits;         // k-splits per split tile (1 = none)
   int kb_per_split;
+  int split_from_tile;  // tiles with a linear index >= this are k-split; earlier tiles are whole
+  int narrow_from_tile; // tiles >= this are done as two half-width units (no reduction needed)
+  uint32_t idesc_narrow; // instruction descriptor with N = BN / 2 for those units
   int total_units;    // batch * m_tiles * n_tiles * splits
   int group_m;        // raster: m-tiles per group
   int is_bf16;        // output / operand type: 1 bf16, 0 fp16
@@ -158,13 +161,35 @@ struct BoundedWait {
 
 struct WorkUnit {
   int batch, m0, n0, kb0, kb1, split, row_tile;
+  bool is_split;
+  bool is_narrow;  // covers only OUT_BN / 2 columns starting at n0
 };
 
 template <class T>
 __device__ __forceinline__ WorkUnit decode_unit(const KernelParams& p, int unit, int cta_rank) {
   WorkUnit w;
-  const int split = unit % p.splits;
-  int tile = unit / p.splits;
+  // Units [0, split_from_tile) are whole tiles; the rest are (tile, k-split) pairs.
+  int tile, split;
+  int half = 0;
+  w.is_narrow = false;
+  if (unit >= p.narrow_from_tile) {
+    // Two half-width units per tile (never combined with k-splitting).
+    const int u = unit - p.narrow_from_tile;
+    tile = p.narrow_from_tile + (u >> 1);
+    half = u & 1;
+    split = 0;
+    w.is_split = false;
+    w.is_narrow = true;
+  } else if (unit < p.split_from_tile) {
+    tile = unit;
+    split = 0;
+    w.is_split = false;
+  } else {
+    const int u = unit - p.split_from_tile;
+    tile = p.split_from_tile + u / p.splits;
+    split = u - (u / p.splits) * p.splits;
+    w.is_split = p.splits > 1;
+  }
   const int tiles_per_batch = p.m_tiles * p.n_tiles;
   w.batch = tile / tiles_per_batch;
   const int t = tile - w.batch * tiles_per_batch;
@@ -176,12 +201,17 @@ __device__ __forceinline__ WorkUnit decode_unit(const KernelParams& p, int unit,
   const int m_t = first_m + r % rows_in_group;
   const int n_t = r / rows_in_group;
   w.m0 = (m_t * T::CTA_GROUP + cta_rank) * T::BM;
-  w.n0 = n_t * T::OUT_BN;
+  w.n0 = n_t * T::OUT_BN + half * (T::OUT_BN / 2);
   w.split = split;
-  w.kb0 = split * p.kb_per_split;
-  w.kb1 = min(p.k_blocks, w.kb0 + p.kb_per_split);
-  w.row_tile = (w.batch * p.m_tiles + m_t) * T::CTA_GROUP + cta_rank;  // 128-row tile id
-  w.row_tile = w.row_tile * p.n_tiles + n_t;
+  if (w.is_split) {
+    w.kb0 = split * p.kb_per_split;
+    w.kb1 = min(p.k_blocks, w.kb0 + p.kb_per_split);
+  } else {
+    w.kb0 = 0;
+    w.kb1 = p.k_blocks;
+  }
+  // Index of this CTA's 128-row tile among the split tiles (slabs and counters).
+  w.row_tile = (tile - p.split_from_tile) * T::CTA_GROUP + cta_rank;
   return w;
 }
 
@@ -303,7 +333,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
       if (bw.aborted()) break;
       const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
-      const int b_row = (T::EPI == EPI_SWIGLU) ? w.n0 : w.n0 + static_cast<int>(cta_rank) * T::B_ROWS;
+      // A narrow unit needs only the first half of each CTA's B slab; the full box is
+      // still loaded (its tail is ignored by the narrower MMA).
+      const int b_row = (T::EPI == EPI_SWIGLU)
+                            ? w.n0
+                            : w.n0 + static_cast<int>(cta_rank) * (w.is_narrow ? T::B_ROWS / 2 : T::B_ROWS);
       const int b_batch = (T::EPI == EPI_SWIGLU) ? 0 : w.batch;
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
@@ -347,6 +381,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         AYLA_TRACE_WAIT(tr_wait2, bw.wait(bar_acc_empty + acc * 8, acc_phase ^ 1, ST_TIMEOUT_ACC_EMPTY))
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t unit_idesc = w.is_narrow ? p.idesc_narrow : idesc;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL))
           tc_fence_after_sync();
@@ -356,7 +391,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const uint32_t stage_off = stage * (T::STAGE_BYTES >> 4);
 #pragma unroll
             for (int k4 = 0; k4 < T::BK / 16; ++k4) {
-              umma_f16<CG>(tmem_d, desc_a0 + (stage_off + 2 * k4), desc_b0 + (stage_off + 2 * k4), idesc,
+              umma_f16<CG>(tmem_d, desc_a0 + (stage_off + 2 * k4), desc_b0 + (stage_off + 2 * k4), unit_idesc,
                            (kb > w.kb0 || k4 > 0) ? 1u : 0u);
             }
             if constexpr (CG == 1) {
@@ -405,7 +440,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // once) and the results are garbage that the status word disowns.
     for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
       const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
-      const bool split_k = p.splits > 1;
+      const bool split_k = w.is_split;
 
       if constexpr (T::EPI == EPI_BIAS && !T::TRANS_OUT) {
         // Stage this tile's bias slice as fp32; double buffered so one barrier per
@@ -421,6 +456,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL))
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+
+      const bool rows_live = (w.m0 + q * 32) < p.m;
 
       // Finish one chunk of up to 32 fp32 values of this thread's row (bias, round,
       // store).  `c32` indexes 32-column chunks of the output tile.
@@ -483,49 +520,83 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       };
 
-      const bool rows_live = (w.m0 + q * 32) < p.m;
+      // Hand the accumulator buffer back to the MMA warp (all of it is in registers).
+      auto release_accumulator = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 2) {
+            mbar_arrive_cluster(acc_empty_leader + acc * 8);
+          } else {
+            mbar_arrive(bar_acc_empty + acc * 8);
+          }
+        }
+      };
 
       if (!split_k) {
-#pragma unroll 1
-        for (int c32 = 0; c32 < CHUNKS32; ++c32) {
-          const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
-          float v[32];
-          if constexpr (T::EPI == EPI_SWIGLU) {
-            uint32_t g[32], u[32];
-            tmem_ld_32x32(t_acc + c32 * 32, g);
-            tmem_ld_32x32(t_acc + T::OUT_BN + c32 * 32, u);
-            tmem_ld_wait();
+        if constexpr (!T::TRANS_OUT) {
+          // Software-pipelined over 32-column chunks: the TMEM load of chunk c+1 is in
+          // flight while chunk c is converted, staged and stored.
+          constexpr int REGS = (T::EPI == EPI_SWIGLU) ? 64 : 32;
+          uint32_t ra[REGS], rb[REGS];
+          auto issue = [&](int c32, uint32_t (&r)[REGS]) {
+            if constexpr (T::EPI == EPI_SWIGLU) {
+              tmem_ld_32x32(t_acc + c32 * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+              tmem_ld_32x32(t_acc + T::OUT_BN + c32 * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            } else {
+              tmem_ld_32x32(t_acc + c32 * 32, r);
+            }
+          };
+          auto consume = [&](int c32, uint32_t (&r)[REGS]) {
+            // Liveness per 64 columns: both halves of a 128-byte store row go together.
+            if (!(rows_live && (w.n0 + (c32 >> 1) * 64) < p.n)) return;
+            float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
-          } else if constexpr (CHUNK_COLS == 32) {
-            uint32_t r[32];
-            tmem_ld_32x32(t_acc + c32 * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          } else {
-            uint32_t r[16];
-            tmem_ld_32x16(t_acc, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-          }
-          if (c32 == CHUNKS32 - 1) {
-            // Whole accumulator is in registers: hand the TMEM buffer back.
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-              if constexpr (CG == 2) {
-                mbar_arrive_cluster(acc_empty_leader + acc * 8);
+            for (int j = 0; j < 32; ++j) {
+              if constexpr (T::EPI == EPI_SWIGLU) {
+                v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r[32 + j]));
               } else {
-                mbar_arrive(bar_acc_empty + acc * 8);
+                v[j] = __uint_as_float(r[j]);
               }
             }
+            finish_chunk(v, c32);
+          };
+          const int unit_chunks = w.is_narrow ? CHUNKS32 / 2 : CHUNKS32;
+          issue(0, ra);
+#pragma unroll 1
+          for (int c32 = 0; c32 < unit_chunks; c32 += 2) {
+            tmem_ld_wait();
+            issue(c32 + 1, rb);
+            consume(c32, ra);
+            tmem_ld_wait();
+            if (c32 + 2 < unit_chunks) {
+              issue(c32 + 2, ra);
+            } else {
+              release_accumulator();
+            }
+            consume(c32 + 1, rb);
           }
-          // The pairing of 32-column halves into one 64-column store needs both
-          // halves handled alike, so liveness is decided per 64 columns.
-          const bool live64 = rows_live && (w.n0 + (c32 >> 1) * 64) < p.n;
-          if (T::TRANS_OUT ? live : live64) finish_chunk(v, c32);
+        } else {
+#pragma unroll 1
+          for (int c32 = 0; c32 < CHUNKS32; ++c32) {
+            const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
+            float v[32];
+            if constexpr (CHUNK_COLS == 32) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_acc + c32 * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            } else {
+              uint32_t r[16];
+              tmem_ld_32x16(t_acc, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            }
+            if (c32 == CHUNKS32 - 1) release_accumulator();
+            if (live) finish_chunk(v, c32);
+          }
         }
       } else {
         // ---- split-K: park the fp32 partial, last arriver of the tile reduces.
@@ -558,15 +629,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               }
             }
           }
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (CG == 2) {
-              mbar_arrive_cluster(acc_empty_leader + acc * 8);
-            } else {
-              mbar_arrive(bar_acc_empty + acc * 8);
-            }
-          }
+          release_accumulator();
           __threadfence();
           named_bar_sync(2, 128);
           if (epi_tid == 0) {

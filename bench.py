@@ -81,7 +81,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
@@ -239,43 +239,21 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-def swiglu_extra(steps: int, peaks: dict) -> dict:
-    """Fused SwiGLU x[8192,4096], W[14336,4096] (operands 537 MB > L2) vs the unfused torch path."""
-    from ayla_b200 import _lib
+def swiglu_extra(peaks: dict) -> dict:
+    """Fused SwiGLU x[8192,4096], W[14336,4096] (operands 537 MB > L2) against the two torch
+    formulations (two mm + eager epilogue; one mm on the concatenated weight + epilogue)."""
+    from ayla_b200.suite import measure_swiglu
 
-    dev = "cuda"
-    m, n, k = 8192, 14336, 4096
-    g = torch.Generator(device="cpu").manual_seed(5)
-    x = torch.randn(m, k, generator=g).bfloat16().to(dev)
-    wg = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(dev)
-    wu = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(dev)
-    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-    stream = torch.cuda.current_stream().cuda_stream
-
-    def ours(_):
-        _lib.swiglu("bfloat16", x.data_ptr(), wg.data_ptr(), wu.data_ptr(), out.data_ptr(), m, n, k, None, 0, stream)
-
-    def unfused(_):
-        torch.nn.functional.silu(torch.mm(x, wg.t())) * torch.mm(x, wu.t())
-
-    for _ in range(3):
-        ours(0)
-        unfused(0)
-    ms = cuda_time_ms(ours, steps)
-    ms_t = cuda_time_ms(unfused, steps)
-    fl = 4.0 * m * n * k
-    return {
-        "workload": "C4 fused SwiGLU bf16 x[8192,4096] W[14336,4096]",
-        "tflops": fl / ms / 1e9, "ms": ms, "frac_of_measured_bf16_peak": fl / ms / 1e9 / peaks["bf16"],
-        "torch_unfused_tflops": fl / ms_t / 1e9, "torch_unfused_ms": ms_t,
-    }
+    row = measure_swiglu(8192, 14336, 4096, peaks)
+    row["workload"] = "C4 fused SwiGLU bf16 x[8192,4096] W_gate,W_up[14336,4096]"
+    return row
 
 
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
-    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--steps", type=int, default=2000)
+    parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--suite", action="store_true")
     parser.add_argument("--no-extra", action="store_true")
@@ -403,7 +381,7 @@ def main() -> None:
                 cublas(i)
             ms_t = cuda_time_ms(cublas, args.steps)
             line["extra"] = {"torch_mm_tflops": FLOPS / ms_t / 1e9, "torch_mm_ms": ms_t,
-                             "swiglu": swiglu_extra(max(5, args.steps // 10), peaks)}
+                             "swiglu": swiglu_extra(peaks)}
     else:
         line["sharded"] = sharded_results(args, rank, world, device)
         import torch.distributed as dist

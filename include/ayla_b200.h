@@ -64,6 +64,8 @@ typedef struct ayla_b200_config {
   int32_t grid_ctas; /* persistent grid size, 0 = one CTA per SM (capped by the work) */
   int32_t l2_hint_a; /* 0 normal, 1 evict_first, 2 evict_last; a/bt as passed by the caller */
   int32_t l2_hint_b;
+  int32_t split_tail; /* wave quantisation: 1 = apply split_k only to the tiles of the last, partial
+                         wave; 2 = do those tiles as two half-width units each (split_k must be 1) */
 } ayla_b200_config;
 
 /*

@@ -72,7 +72,13 @@ def test_default_config_validates_shapes(args, code):
 
 def test_default_schedules_for_the_benchmark_shapes():
     big = _lib.default_config("mm", "bfloat16", 1, 4096, 4096, 4096)
-    assert (big.tile_n, big.cta_group, big.swap_ab, big.split_k) == (256, 2, 0, 1)
+    # 256 paired tiles on 74 SM pairs = 3.46 waves: the 34 tiles of the last wave run at half width
+    assert (big.tile_n, big.cta_group, big.swap_ab, big.split_k, big.split_tail) == (256, 2, 0, 1, 2)
+    assert _lib.workspace_bytes(big, "mm", 1, 4096, 4096, 4096) == 0
+    ksplit = _lib.Config.from_dict(dict(tile_n=256, cta_group=2, split_k=2, split_tail=1))
+    assert _lib.workspace_bytes(ksplit, "mm", 1, 4096, 4096, 4096) == 65536 + 34 * 2 * 2 * 128 * 256 * 4
+    whole = _lib.default_config("mm", "bfloat16", 1, 8192, 8192, 8192)  # 13.8 waves: no split
+    assert (whole.split_k, whole.split_tail) == (1, 0)
     decode = _lib.default_config("mm", "bfloat16", 1, 1, 4096, 4096)
     assert decode.swap_ab == 1 and decode.tile_n == 16 and decode.split_k >= 2
     m64 = _lib.default_config("mm", "bfloat16", 1, 64, 14336, 4096)
