@@ -1,0 +1,184 @@
+"""Route ``aten.mm/addmm/bmm`` in ``torch.compile`` graphs to the sm_100a GEMM ops.
+
+Same contract as the reference's Inductor integration (ayla/torch_compile.py:652-775):
+``install()`` claims contiguous NT-layout fp16/bf16 GEMMs on CUDA -- ``lhs`` contiguous,
+``rhs`` a transposed view of a contiguous ``bt`` (strides ``(1, k)``, or ``(n*k, 1, k)`` for
+bmm), static sizes, 1-D bias of length n with ``alpha == beta == 1`` -- and leaves
+everything else to stock Inductor; ``uninstall()`` hands them back.  ``install()`` is
+idempotent and registers all six ``jit_*`` ops up front (ayla/torch_compile.py:743-749).
+
+The mechanism differs because the Inductor of this torch (2.11) has no ``user_lowerings``
+hook (the reference's file does not import here): the claim is made by a post-grad FX
+pass (``torch._inductor.config.post_grad_custom_post_pass``) that rewrites a claimed node
+into a call of the functional form of the op, ``torch.ops.ayla.jit_{op}_{dtype}_fn(a, bt)``,
+which Inductor then emits as an extern kernel call.  The pass carries a ``uuid`` so
+Inductor's code cache keys on it.
+"""
+
+from __future__ import annotations
+
+from functools import cache
+
+import torch
+from torch._inductor import config as inductor_config
+from torch._inductor.custom_graph_pass import CustomGraphPass, get_hash_for_files
+
+from .gemm_jit import _SHORT_DTYPES, _TORCH_DTYPES, gemm_jit_compiler, gemm_op, select_gemm_schedule
+from .torch_custom_call import DEFAULT_NAMESPACE, OperandKind, make_torch_custom_call
+
+aten = torch.ops.aten
+_DTYPE_NAMES = {torch.float16: "float16", torch.bfloat16: "bfloat16"}
+
+
+@cache
+def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
+    """Functional form ``(bias?, a, bt) -> out`` of ``gemm_op`` (the result is allocated by
+    the op), the form a functional FX graph can hold.  Counterpart of the reference's
+    allocating ops (ayla/gemm_collection/dynamic_m.py:90-121)."""
+    compiler = gemm_jit_compiler(operation, dtype)
+
+    def infer(*inputs: torch.Tensor):
+        a, bt = inputs[-2], inputs[-1]
+        return [(*a.shape[:-1], bt.shape[-2])]
+
+    inputs = 3 if operation == "addmm" else 2
+    return make_torch_custom_call(
+        compiler,
+        [OperandKind.R] * inputs + [OperandKind.RESULT],
+        namespace=namespace,
+        name=f"jit_{operation}_{_SHORT_DTYPES[dtype]}_fn",
+        infer_result_shapes=infer,
+    )
+
+
+def _static_ints(values) -> tuple[int, ...] | None:
+    out = []
+    for v in values:
+        if not isinstance(v, int):
+            return None
+        out.append(v)
+    return tuple(out)
+
+
+def _val(node):
+    val = node.meta.get("val") if isinstance(node, torch.fx.Node) else None
+    return val if isinstance(val, torch.Tensor) else None
+
+
+def _claim(operation: str, lhs, rhs, bias=None) -> tuple[str, tuple[int, ...]] | None:
+    """Decide whether this GEMM is ours: returns (dtype name, (batch?, m, n, k)) or None."""
+    lv, rv = _val(lhs), _val(rhs)
+    if lv is None or rv is None:
+        return None
+    dtype = _DTYPE_NAMES.get(lv.dtype)
+    if lv.device.type != "cuda" or dtype is None or rv.dtype != lv.dtype or rv.device != lv.device:
+        return None
+    rank = 3 if operation == "bmm" else 2
+    if lv.dim() != rank or rv.dim() != rank:
+        return None
+    lsize, rsize = _static_ints(lv.shape), _static_ints(rv.shape)
+    lstride, rstride = _static_ints(lv.stride()), _static_ints(rv.stride())
+    if None in (lsize, rsize, lstride, rstride):
+        return None  # dynamic shapes are left to Inductor
+    *batch, m, k = lsize
+    n = rsize[-1]
+    if rsize[-2] != k or list(rsize[:-2]) != batch:
+        return None
+    # A row-major a and a column-major b: a @ bt^T with contiguous bt.
+    contiguous = (m * k, k, 1)[-rank:]
+    if lstride != contiguous:
+        return None
+    if rstride != (*([n * k] if batch else []), 1, k):
+        return None
+    if bias is not None:
+        bv = _val(bias)
+        if bv is None or bv.dtype != lv.dtype or _static_ints(bv.shape) != (n,) or bv.device != lv.device:
+            return None
+        if _static_ints(bv.stride()) != (1,):
+            return None
+    if select_gemm_schedule(operation, dtype, m, n, k, *batch) is None:
+        return None
+    return dtype, (*batch, m, n, k)
+
+
+def route_gemms(graph: torch.fx.Graph) -> int:
+    """Rewrite every claimed ``aten.mm/addmm/bmm`` node of ``graph``; returns how many."""
+    rewritten = 0
+    for node in list(graph.nodes):
+        if node.op != "call_function":
+            continue
+        if node.target is aten.mm.default and len(node.args) == 2:
+            operation, (lhs, rhs), bias = "mm", node.args, None
+        elif node.target is aten.bmm.default and len(node.args) == 2:
+            operation, (lhs, rhs), bias = "bmm", node.args, None
+        elif node.target is aten.addmm.default and len(node.args) == 3:
+            if node.kwargs.get("beta", 1) != 1 or node.kwargs.get("alpha", 1) != 1:
+                continue
+            operation, (bias, lhs, rhs) = "addmm", node.args
+        else:
+            continue
+        claim = _claim(operation, lhs, rhs, bias)
+        if claim is None:
+            continue
+        dtype, _ = claim
+        op = gemm_fn_op(operation, dtype)
+        with graph.inserting_before(node):
+            # bt is the transposed view of rhs: contiguous by the stride check above.
+            perm = [0, 2, 1] if operation == "bmm" else [1, 0]
+            bt = graph.call_function(aten.permute.default, (rhs, perm))
+            rv = _val(rhs)
+            bt.meta["val"] = rv.permute(perm)
+            args = (lhs, bt) if bias is None else (bias, lhs, bt)
+            new = graph.call_function(op, args)
+            new.meta.update({k: v for k, v in node.meta.items() if k != "original_aten"})
+        node.replace_all_uses_with(new)
+        graph.erase_node(node)
+        rewritten += 1
+    if rewritten:
+        graph.eliminate_dead_code()
+    return rewritten
+
+
+class AylaRoutingPass(CustomGraphPass):
+    """Post-grad pass: ours first, then whatever pass was installed before."""
+
+    def __init__(self, previous=None):
+        self.previous = previous
+
+    def __call__(self, graph: torch.fx.Graph) -> None:
+        route_gemms(graph)
+        if self.previous is not None:
+            self.previous(graph)
+
+    def uuid(self):
+        previous = self.previous.uuid() if isinstance(self.previous, CustomGraphPass) else None
+        return ("ayla_b200.routing", get_hash_for_files((__file__,)), previous)
+
+
+_installed: AylaRoutingPass | None = None
+
+
+def install() -> None:
+    """Claim the GEMMs.  Idempotent."""
+    global _installed
+    # Register the ops up front: a cached graph can call one without this process ever
+    # running the pass that would create it.
+    for operation in ("mm", "addmm", "bmm"):
+        for dtype in _TORCH_DTYPES:
+            gemm_op(operation, dtype)
+            gemm_fn_op(operation, dtype)
+    current = inductor_config.post_grad_custom_post_pass
+    if _installed is not None and current is _installed:
+        return
+    _installed = AylaRoutingPass(previous=current)
+    inductor_config.post_grad_custom_post_pass = _installed
+
+
+def uninstall() -> None:
+    """Hand the GEMMs back.  Stands down if someone else has replaced the pass since."""
+    global _installed
+    if _installed is None:
+        return
+    if inductor_config.post_grad_custom_post_pass is _installed:
+        inductor_config.post_grad_custom_post_pass = _installed.previous
+    _installed = None

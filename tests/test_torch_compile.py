@@ -1,0 +1,147 @@
+"""Routing decisions of ``ayla_b200.torch_compile`` (mirrors the reference's
+tests/test_torch_compile.py:140-157 and tests/test_gemm_jit.py:77-98).  The decision
+logic is exercised on CPU with fake CUDA tensors; the end-to-end compile runs on a GPU."""
+
+import pytest
+import torch
+from torch._inductor import config as inductor_config
+from torch._inductor.decomposition import select_decomp_table
+from torch._subclasses.fake_tensor import FakeTensorMode
+from torch.fx.experimental.proxy_tensor import make_fx
+
+from ayla_b200 import torch_compile as tc
+
+aten = torch.ops.aten
+
+
+def trace(fn, *specs):
+    """FX graph of fn over fake tensors described by (shape, dtype, device) specs."""
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        args = [torch.empty(shape, dtype=dtype, device=device) for shape, dtype, device in specs]
+        return make_fx(fn, decomposition_table=select_decomp_table(), tracing_mode="real")(*args)
+
+
+def targets(gm):
+    return [n.target for n in gm.graph.nodes if n.op == "call_function"]
+
+
+BF16, F16, F32 = torch.bfloat16, torch.float16, torch.float32
+
+
+def test_supported_gemms_are_claimed():
+    gm = trace(lambda a, bt: torch.mm(a, bt.t()), ((96, 128), BF16, "cuda"), ((128, 128), BF16, "cuda"))
+    assert tc.route_gemms(gm.graph) == 1
+    assert torch.ops.ayla.jit_mm_bf16_fn.default in targets(gm) and aten.mm.default not in targets(gm)
+
+    gm = trace(lambda bias, a, bt: torch.addmm(bias, a, bt.t()),
+               ((128,), F16, "cuda"), ((96, 128), F16, "cuda"), ((128, 128), F16, "cuda"))
+    assert tc.route_gemms(gm.graph) == 1
+    assert torch.ops.ayla.jit_addmm_f16_fn.default in targets(gm)
+
+    gm = trace(lambda a, bt: torch.bmm(a, bt.transpose(-1, -2)),
+               ((2, 96, 128), BF16, "cuda"), ((2, 128, 128), BF16, "cuda"))
+    assert tc.route_gemms(gm.graph) == 1
+    assert torch.ops.ayla.jit_bmm_bf16_fn.default in targets(gm)
+    gm.graph.lint()
+
+
+@pytest.mark.parametrize(
+    "fn, specs",
+    [
+        # CPU tensors
+        (lambda a, bt: torch.mm(a, bt.t()), [((96, 128), BF16, "cpu"), ((128, 128), BF16, "cpu")]),
+        # float32
+        (lambda a, bt: torch.mm(a, bt.t()), [((96, 128), F32, "cuda"), ((128, 128), F32, "cuda")]),
+        # rhs is a plain contiguous [k, n] matrix, not a transposed view of bt
+        (lambda a, b: torch.mm(a, b), [((96, 128), BF16, "cuda"), ((128, 64), BF16, "cuda")]),
+        # non-contiguous lhs
+        (lambda a, bt: torch.mm(a.t(), bt.t()), [((128, 96), BF16, "cuda"), ((128, 128), BF16, "cuda")]),
+        # n not a multiple of 8: no schedule
+        (lambda a, bt: torch.mm(a, bt.t()), [((96, 128), BF16, "cuda"), ((60, 128), BF16, "cuda")]),
+        # scaled addmm
+        (lambda bias, a, bt: torch.addmm(bias, a, bt.t(), alpha=2.0),
+         [((128,), BF16, "cuda"), ((96, 128), BF16, "cuda"), ((128, 128), BF16, "cuda")]),
+        # bias that is not [n]
+        (lambda bias, a, bt: torch.addmm(bias, a, bt.t()),
+         [((96, 128), BF16, "cuda"), ((96, 128), BF16, "cuda"), ((128, 128), BF16, "cuda")]),
+    ],
+)
+def test_unsupported_gemms_are_declined(fn, specs):
+    gm = trace(fn, *specs)
+    before = targets(gm)
+    assert tc.route_gemms(gm.graph) == 0
+    assert targets(gm) == before
+
+
+def test_install_is_idempotent_and_uninstall_restores():
+    previous = inductor_config.post_grad_custom_post_pass
+    try:
+        tc.install()
+        first = inductor_config.post_grad_custom_post_pass
+        assert isinstance(first, tc.AylaRoutingPass) and first.previous is previous
+        tc.install()
+        assert inductor_config.post_grad_custom_post_pass is first
+        assert first.uuid() == first.uuid()
+        for operation in ("mm", "addmm", "bmm"):
+            for short in ("f16", "bf16"):
+                assert hasattr(torch.ops.ayla, f"jit_{operation}_{short}")
+                assert hasattr(torch.ops.ayla, f"jit_{operation}_{short}_fn")
+        tc.uninstall()
+        assert inductor_config.post_grad_custom_post_pass is previous
+        # someone else claims the hook after us: stand down without touching it
+        tc.install()
+        other = lambda graph: None  # noqa: E731
+        inductor_config.post_grad_custom_post_pass = other
+        tc.uninstall()
+        assert inductor_config.post_grad_custom_post_pass is other
+    finally:
+        inductor_config.post_grad_custom_post_pass = previous
+        tc.uninstall()
+
+
+@pytest.fixture
+def ayla_installed():
+    tc.install()
+    try:
+        yield
+    finally:
+        tc.uninstall()
+        torch._dynamo.reset()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("operation", ["mm", "addmm", "bmm"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_torch_compile_routes_supported_gemms_to_jit(operation, dtype, ayla_installed):
+    """tests/test_gemm_jit.py:77-98 of the reference."""
+    from torch._inductor.utils import run_and_get_code
+
+    lead = (2,) if operation == "bmm" else ()
+    a = torch.randn((*lead, 96, 128), device="cuda", dtype=dtype)
+    bt = torch.randn((*lead, 128, 128), device="cuda", dtype=dtype)
+    bias = torch.randn(128, device="cuda", dtype=dtype)
+
+    def compute(a, bt, bias):
+        if operation == "addmm":
+            return torch.addmm(bias, a, bt.T)
+        if operation == "bmm":
+            return torch.bmm(a, bt.transpose(-1, -2))
+        return torch.mm(a, bt.T)
+
+    with torch.no_grad(), inductor_config.patch(force_disable_caches=True):
+        actual, code = run_and_get_code(torch.compile(compute, fullgraph=True, dynamic=False), a, bt, bias)
+        expected = compute(a, bt, bias)
+    torch.testing.assert_close(actual, expected, atol=0.125, rtol=0.02)
+    assert any(f"jit_{operation}_" in source for source in code)
+
+
+@pytest.mark.gpu
+def test_torch_compile_declines_cpu_and_plain_layout(ayla_installed):
+    from torch._inductor.utils import run_and_get_code
+
+    a = torch.randn(96, 128, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad(), inductor_config.patch(force_disable_caches=True):
+        actual, code = run_and_get_code(torch.compile(lambda x, y: torch.mm(x, y), dynamic=False), a, b)
+    torch.testing.assert_close(actual, a @ b, atol=0.125, rtol=0.02)
+    assert not any("jit_mm_" in source for source in code)
