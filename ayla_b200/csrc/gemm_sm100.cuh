@@ -6,11 +6,11 @@
 // (ayla/gemm_jit.py:267-307): fp16/bf16 inputs, fp32 accumulation, one rounding
 // to the output type at the end (ayla/passes/lower_to_ptx_template.py:134-149).
 //
-// One CTA = 6 warps:
+// One CTA = 10 warps:
 //   warp 0      TMA producer  : global -> shared ring of STAGES (A 128x64, B BNx64) slabs
 //   warp 1      MMA issuer    : tcgen05.mma from shared into a TMEM accumulator;
 //                               also owns the TMEM allocation
-//   warps 2..5  epilogue      : TMEM -> registers -> (bias | SiLU*up) -> round ->
+//   warps 2..9  epilogue      : TMEM -> registers -> (bias | SiLU*up) -> round ->
 //                               swizzled shared -> TMA store   (or direct stores for the
 //                               transposed / split-K forms)
 // The accumulator is double buffered in TMEM so the epilogue of one tile runs
@@ -108,13 +108,13 @@ struct GemmTraits {
                                    : TMEM_COLS_NEEDED <= 128 ? 128
                                    : TMEM_COLS_NEEDED <= 256 ? 256
                                                              : 512;
-  static constexpr int EPI_WARPS = 4;
+  static constexpr int EPI_WARPS = 8;
   static constexpr int STORE_BUF_BYTES = 32 * 128;  // 32 rows x 64 columns of 16-bit
-  static constexpr int STORE_BYTES = TRANS_OUT ? 0 : EPI_WARPS * 2 * STORE_BUF_BYTES;
+  static constexpr int STORE_BYTES = TRANS_OUT ? 0 : EPI_WARPS * STORE_BUF_BYTES;
   static constexpr int BIAS_BYTES = (EPI == EPI_BIAS && !TRANS_OUT) ? 2 * BN * 4 : 0;
   static constexpr int MISC_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BIAS_BYTES + MISC_BYTES;
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 64 + EPI_WARPS * 32;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05 N extent");
   static_assert(B_BYTES % 1024 == 0, "B slab must keep the 1024-byte swizzle alignment");
   static_assert(EPI != EPI_SWIGLU || (BN == 256 && !TRANS_OUT), "SwiGLU uses the 2x128 layout");
@@ -421,23 +421,28 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int q = warp & 3;                        // TMEM lane quarter this warp may read
-    const int epi_tid = (warp - 2) * 32 + lane;    // 0..127
+    // Eight warps: warp w may read TMEM lanes [32 * (w % 4), +32), so two warps share
+    // each lane quarter and take alternate 64-column groups of the tile.  One warp per
+    // scheduler is latency-bound on its own dependent instruction stream; two hide
+    // each other's TMEM-load, conversion and store latencies.
+    const int q = warp & 3;                          // TMEM lane quarter
+    const int wsub = (warp - 2) >> 2;                // 0 / 1: which 64-column groups
+    const int epi_tid = (warp - 2) * 32 + lane;      // 0..255
     const int row_in_tile = q * 32 + lane;
     const int is_bf16 = p.is_bf16;
-    uint8_t* my_store = smem_store + (warp - 2) * 2 * T::STORE_BUF_BYTES;
-    uint32_t store_buf = 0;
+    uint8_t* my_store = smem_store + (warp - 2) * T::STORE_BUF_BYTES;
     uint32_t acc = 0, acc_phase = 0;
     uint32_t bias_buf = 0;
     constexpr int CHUNKS32 = T::OUT_BN / 32 > 0 ? T::OUT_BN / 32 : 1;  // 32-column chunks
     constexpr int CHUNK_COLS = T::OUT_BN < 32 ? T::OUT_BN : 32;
+    constexpr int EPI_THREADS = T::EPI_WARPS * 32;
     const uint32_t acc_empty_leader =
         (CG == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
     AYLA_TRACE_BEGIN
 
-    // No early exit in this loop: the four warps meet at named barriers, so after
-    // an abort they keep walking the units together (every wait then returns at
-    // once) and the results are garbage that the status word disowns.
+    // No early exit in this loop: the warps meet at named barriers, so after an abort
+    // they keep walking the units together (every wait then returns at once) and the
+    // results are garbage that the status word disowns.
     for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
       const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
       const bool split_k = w.is_split;
@@ -446,11 +451,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         // Stage this tile's bias slice as fp32; double buffered so one barrier per
         // tile is enough.
         float* bdst = smem_bias + bias_buf * BN;
-        for (int c = epi_tid; c < BN; c += 128) {
+        for (int c = epi_tid; c < BN; c += EPI_THREADS) {
           const int col = w.n0 + c;
           bdst[c] = (col < p.n) ? load_elem(p.bias, col, is_bf16) : 0.0f;
         }
-        named_bar_sync(1, 128);
+        named_bar_sync(1, EPI_THREADS);
       }
 
       AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL))
@@ -458,6 +463,22 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 
       const bool rows_live = (w.m0 + q * 32) < p.m;
+      const int unit_chunks = w.is_narrow ? CHUNKS32 / 2 : CHUNKS32;
+      const int unit_groups = (unit_chunks + 1) / 2;
+
+      // Hand the accumulator buffer back to the MMA warp (every warp arrives once per
+      // unit, after its last TMEM load has completed).
+      auto release_accumulator = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 2) {
+            mbar_arrive_cluster(acc_empty_leader + acc * 8);
+          } else {
+            mbar_arrive(bar_acc_empty + acc * 8);
+          }
+        }
+      };
 
       // Finish one chunk of up to 32 fp32 values of this thread's row (bias, round,
       // store).  `c32` indexes 32-column chunks of the output tile.
@@ -491,52 +512,47 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           }
           // Two 32-column chunks fill one 64-column (128-byte) store row.
           const int half = c32 & 1;
-          uint8_t* buf = my_store + store_buf * T::STORE_BUF_BYTES;
           if (half == 0) {
-            // The bulk store issued from this buffer two stores ago must have read it.
-            if (lane == 0) tma_store_wait_read<1>();
+            // The bulk store this warp issued last must have finished reading the buffer.
+            if (lane == 0) tma_store_wait_read<0>();
             __syncwarp();
+          }
+          uint32_t pk[CHUNK_COLS / 2];
+          if (is_bf16) {
+#pragma unroll
+            for (int j = 0; j < CHUNK_COLS / 2; ++j) {
+              __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              pk[j] = *reinterpret_cast<uint32_t*>(&t);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CHUNK_COLS / 2; ++j) {
+              __half2 t = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+              pk[j] = *reinterpret_cast<uint32_t*>(&t);
+            }
           }
 #pragma unroll
           for (int j = 0; j < CHUNK_COLS / 8; ++j) {
-            uint4 pk;
-            pk.x = pack2(v[8 * j + 0], v[8 * j + 1], is_bf16);
-            pk.y = pack2(v[8 * j + 2], v[8 * j + 3], is_bf16);
-            pk.z = pack2(v[8 * j + 4], v[8 * j + 5], is_bf16);
-            pk.w = pack2(v[8 * j + 6], v[8 * j + 7], is_bf16);
             const int chunk16 = half * 4 + j;  // 16-byte chunk within the 128-byte row
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk16 ^ (lane & 7)) << 4)) = pk;
+            *reinterpret_cast<uint4*>(my_store + lane * 128 + ((chunk16 ^ (lane & 7)) << 4)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
           }
-          const bool last_half = (half == 1) || (c32 == CHUNKS32 - 1);
-          if (last_half) {
+          if (half == 1) {
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&tm_d, smem_u32(buf), w.n0 + (c32 >> 1) * 64, w.m0 + q * 32, w.batch);
+              tma_store_3d(&tm_d, smem_u32(my_store), w.n0 + (c32 >> 1) * 64, w.m0 + q * 32, w.batch);
               tma_store_commit();
             }
-            store_buf ^= 1;
-          }
-        }
-      };
-
-      // Hand the accumulator buffer back to the MMA warp (all of it is in registers).
-      auto release_accumulator = [&]() {
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (CG == 2) {
-            mbar_arrive_cluster(acc_empty_leader + acc * 8);
-          } else {
-            mbar_arrive(bar_acc_empty + acc * 8);
           }
         }
       };
 
       if (!split_k) {
         if constexpr (!T::TRANS_OUT) {
-          // Software-pipelined over 32-column chunks: the TMEM load of chunk c+1 is in
-          // flight while chunk c is converted, staged and stored.
+          // This warp's 64-column groups, software-pipelined over 32-column chunks: the
+          // TMEM load of the next chunk is in flight while this one is converted,
+          // staged and stored.
           constexpr int REGS = (T::EPI == EPI_SWIGLU) ? 64 : 32;
           uint32_t ra[REGS], rb[REGS];
           auto issue = [&](int c32, uint32_t (&r)[REGS]) {
@@ -561,24 +577,28 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
             finish_chunk(v, c32);
           };
-          const int unit_chunks = w.is_narrow ? CHUNKS32 / 2 : CHUNKS32;
-          issue(0, ra);
+          if (wsub >= unit_groups) {
+            release_accumulator();
+          } else {
+            issue(2 * wsub, ra);
 #pragma unroll 1
-          for (int c32 = 0; c32 < unit_chunks; c32 += 2) {
-            tmem_ld_wait();
-            issue(c32 + 1, rb);
-            consume(c32, ra);
-            tmem_ld_wait();
-            if (c32 + 2 < unit_chunks) {
-              issue(c32 + 2, ra);
-            } else {
-              release_accumulator();
+            for (int g = wsub; g < unit_groups; g += 2) {
+              tmem_ld_wait();
+              issue(2 * g + 1, rb);
+              consume(2 * g, ra);
+              tmem_ld_wait();
+              if (g + 2 < unit_groups) {
+                issue(2 * (g + 2), ra);
+              } else {
+                release_accumulator();
+              }
+              consume(2 * g + 1, rb);
             }
-            consume(c32 + 1, rb);
           }
         } else {
+          // Transposed form: chunks alternate between the two warps of a lane quarter.
 #pragma unroll 1
-          for (int c32 = 0; c32 < CHUNKS32; ++c32) {
+          for (int c32 = wsub; c32 < CHUNKS32; c32 += 2) {
             const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
             float v[32];
             if constexpr (CHUNK_COLS == 32) {
@@ -594,79 +614,88 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
             }
-            if (c32 == CHUNKS32 - 1) release_accumulator();
+            if (c32 + 2 >= CHUNKS32) release_accumulator();
             if (live) finish_chunk(v, c32);
           }
+          if (wsub >= CHUNKS32) release_accumulator();
         }
       } else {
         // ---- split-K: park the fp32 partial, last arriver of the tile reduces.
         // Slab layout: float4 index (c4, row) -> c4 * 128 + row, so a warp's
-        // 16-byte accesses are contiguous.
+        // 16-byte accesses are contiguous.  64-column groups (32-column chunks in the
+        // transposed form) alternate between the two warps of a lane quarter.
         if constexpr (T::EPI != EPI_SWIGLU) {
+          constexpr int STEP = T::TRANS_OUT ? 1 : 2;  // chunks handled back to back
           float4* slab = reinterpret_cast<float4*>(p.ws) +
                          (static_cast<size_t>(w.row_tile) * p.splits + w.split) * (32 * BN);
 #pragma unroll 1
-          for (int c32 = 0; c32 < CHUNKS32; ++c32) {
-            if constexpr (CHUNK_COLS == 32) {
-              uint32_t r[32];
-              tmem_ld_32x32(t_acc + c32 * 32, r);
-              tmem_ld_wait();
+          for (int c0 = wsub * STEP; c0 < CHUNKS32; c0 += 2 * STEP) {
+#pragma unroll 1
+            for (int c32 = c0; c32 < c0 + STEP && c32 < CHUNKS32; ++c32) {
+              if constexpr (CHUNK_COLS == 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_acc + c32 * 32, r);
+                tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                slab[(c32 * 8 + j) * 128 + row_in_tile] =
-                    make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-              }
-            } else {
-              uint32_t r[16];
-              tmem_ld_32x16(t_acc, r);
-              tmem_ld_wait();
+                for (int j = 0; j < 8; ++j) {
+                  slab[(c32 * 8 + j) * 128 + row_in_tile] =
+                      make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                }
+              } else {
+                uint32_t r[16];
+                tmem_ld_32x16(t_acc, r);
+                tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                slab[j * 128 + row_in_tile] =
-                    make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                for (int j = 0; j < 4; ++j) {
+                  slab[j * 128 + row_in_tile] =
+                      make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                }
               }
             }
           }
           release_accumulator();
           __threadfence();
-          named_bar_sync(2, 128);
+          named_bar_sync(2, EPI_THREADS);
           if (epi_tid == 0) {
             const unsigned old = atomicAdd(p.counters + w.row_tile, 1u);
             const bool last = (old == static_cast<unsigned>(p.splits - 1));
             if (last) p.counters[w.row_tile] = 0;  // leave the counter clean for the next launch
             *last_flag = last ? 1u : 0u;
           }
-          named_bar_sync(2, 128);
+          named_bar_sync(2, EPI_THREADS);
           const bool last = *last_flag != 0;
           if (last) {
             __threadfence();
             const float4* tile_slabs = reinterpret_cast<const float4*>(p.ws) +
                                        static_cast<size_t>(w.row_tile) * p.splits * (32 * BN);
 #pragma unroll 1
-            for (int c32 = 0; c32 < CHUNKS32; ++c32) {
-              float v[32];
+            for (int c0 = wsub * STEP; c0 < CHUNKS32; c0 += 2 * STEP) {
+#pragma unroll 1
+              for (int c32 = c0; c32 < c0 + STEP && c32 < CHUNKS32; ++c32) {
+                float v[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-              for (int s = 0; s < p.splits; ++s) {
-                const float4* sl = tile_slabs + static_cast<size_t>(s) * (32 * BN);
+                for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+                for (int s = 0; s < p.splits; ++s) {
+                  const float4* sl = tile_slabs + static_cast<size_t>(s) * (32 * BN);
 #pragma unroll
-                for (int j = 0; j < CHUNK_COLS / 4; ++j) {
-                  const float4 x = __ldcg(sl + (c32 * 8 + j) * 128 + row_in_tile);
-                  v[4 * j + 0] += x.x;
-                  v[4 * j + 1] += x.y;
-                  v[4 * j + 2] += x.z;
-                  v[4 * j + 3] += x.w;
+                  for (int j = 0; j < CHUNK_COLS / 4; ++j) {
+                    const float4 x = __ldcg(sl + (c32 * 8 + j) * 128 + row_in_tile);
+                    v[4 * j + 0] += x.x;
+                    v[4 * j + 1] += x.y;
+                    v[4 * j + 2] += x.z;
+                    v[4 * j + 3] += x.w;
+                  }
                 }
+                const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
+                const bool live64 = rows_live && (w.n0 + (c32 >> 1) * 64) < p.n;
+                if (T::TRANS_OUT ? live : live64) finish_chunk(v, c32);
               }
-              const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
-              const bool live64 = rows_live && (w.n0 + (c32 >> 1) * 64) < p.n;
-              if (T::TRANS_OUT ? live : live64) finish_chunk(v, c32);
             }
           }
-          // All four warps must have read last_flag before the next unit rewrites it.
-          named_bar_sync(2, 128);
+          // Every warp must have read last_flag before the next unit rewrites it.
+          named_bar_sync(2, EPI_THREADS);
         }
       }
 
