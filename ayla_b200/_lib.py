@@ -28,9 +28,11 @@ EXPORTS = (
     "ayla_b200_config_valid",
     "ayla_b200_workspace_bytes",
     "ayla_b200_workspace_counter_bytes",
+    "ayla_b200_copy_2d",
     "ayla_b200_kernel_count",
     "ayla_b200_kernel_info",
     "ayla_b200_set_wait_timeout_ms",
+    "ayla_b200_debug_set_flags",
     "ayla_b200_last_error",
     "ayla_b200_version",
 )
@@ -49,6 +51,7 @@ class Config(ctypes.Structure):
         ("l2_hint_a", ctypes.c_int32),
         ("l2_hint_b", ctypes.c_int32),
         ("split_tail", ctypes.c_int32),
+        ("stream_k", ctypes.c_int32),
     ]
 
     FIELDS = tuple(name for name, _ in _fields_)
@@ -56,7 +59,7 @@ class Config(ctypes.Structure):
     @classmethod
     def from_dict(cls, values: dict) -> "Config":
         cfg = cls(tile_n=256, cta_group=1, swap_ab=0, split_k=1, group_m=8, grid_ctas=0,
-                  l2_hint_a=0, l2_hint_b=0, split_tail=0)
+                  l2_hint_a=0, l2_hint_b=0, split_tail=0, stream_k=0)
         for key in cls.FIELDS:
             if key in values and values[key] is not None:
                 setattr(cfg, key, int(values[key]))
@@ -117,6 +120,8 @@ def load() -> ctypes.CDLL:
         lib.ayla_b200_workspace_bytes.restype = sz
         lib.ayla_b200_workspace_counter_bytes.argtypes = [cfgp, i32, i64, i64, i64, i64]
         lib.ayla_b200_workspace_counter_bytes.restype = sz
+        lib.ayla_b200_copy_2d.argtypes = [vp, sz, vp, sz, sz, sz, vp]
+        lib.ayla_b200_copy_2d.restype = i32
         lib.ayla_b200_kernel_count.argtypes = []
         lib.ayla_b200_kernel_count.restype = i32
         i32p = ctypes.POINTER(ctypes.c_int32)
@@ -124,6 +129,8 @@ def load() -> ctypes.CDLL:
         lib.ayla_b200_kernel_info.restype = i32
         lib.ayla_b200_set_wait_timeout_ms.argtypes = [i64]
         lib.ayla_b200_set_wait_timeout_ms.restype = None
+        lib.ayla_b200_debug_set_flags.argtypes = [i32]
+        lib.ayla_b200_debug_set_flags.restype = None
         lib.ayla_b200_last_error.argtypes = []
         lib.ayla_b200_last_error.restype = ctypes.c_char_p
         lib.ayla_b200_version.argtypes = []
@@ -212,6 +219,12 @@ def gemm_static_scratch(op: str, dtype: str, bias_ptr: int, a_ptr: int, bt_ptr: 
     check(load().ayla_b200_gemm_static_scratch(
         OP_CODES[op], DTYPE_CODES[dtype], bias_ptr or None, a_ptr, bt_ptr, out_ptr, batch, m, n, k,
         ctypes.byref(cfg) if cfg is not None else None, status_ptr or None, stream or None))
+
+
+def copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width_bytes: int, rows: int,
+            stream: int) -> None:
+    """Strided device-to-device copy on the copy engines."""
+    check(load().ayla_b200_copy_2d(dst_ptr, dst_pitch, src_ptr, src_pitch, width_bytes, rows, stream or None))
 
 
 def swiglu(dtype: str, x_ptr: int, wg_ptr: int, wu_ptr: int, out_ptr: int, m: int, n: int, k: int,

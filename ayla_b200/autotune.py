@@ -1,0 +1,229 @@
+"""Measure candidate schedules per shape on a B200 and regenerate the schedule table.
+
+    python -m ayla_b200.autotune --out gpurun_out/autotune.json            # measure (resumable)
+    python -m ayla_b200.autotune --out gpurun_out/autotune.json --emit ayla_b200/gemm_schedule_table.py
+
+The sweep mirrors how the reference's table was produced (per-shape sweeps whose winners are
+stored first, ayla/gemm_schedule_table.py:1-12) and its harness' resume behaviour: results are
+rewritten atomically after every shape and finished shapes are skipped on a re-run
+(benchmarks/oss_gemm_corpus.py:418-442, benchmarks/benchmark_oss_pytorch_gemm_shapes.py:294-318).
+Timing protocol: see :mod:`ayla_b200.suite`.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from pathlib import Path
+
+import torch
+
+from . import _lib
+from .suite import SWEEP_M, SWEEP_NK, _copies, time_interleaved
+
+MAX_WORKSPACE = 512 << 20
+
+BASELINE_SHAPES = [
+    ("mm", "bfloat16", 1, 4096, 4096, 4096),
+    ("mm", "float16", 1, 4096, 4096, 4096),
+    ("mm", "bfloat16", 1, 8192, 8192, 8192),
+    ("addmm", "bfloat16", 1, 8192, 768, 768),
+    ("addmm", "float16", 1, 8192, 768, 768),
+    ("addmm", "bfloat16", 1, 256, 1024, 16384),
+    ("addmm", "float16", 1, 256, 1024, 16384),
+    ("bmm", "bfloat16", 64, 2048, 2048, 128),
+    ("bmm", "bfloat16", 64, 2048, 128, 2048),
+    ("bmm", "bfloat16", 8, 2048, 2048, 128),
+    ("bmm", "bfloat16", 8, 2048, 128, 2048),
+    ("mm", "bfloat16", 1, 4096, 4096, 32768),
+]
+SWEEP_SHAPES = [("mm", "bfloat16", 1, m, n, k) for n, k in SWEEP_NK for m in SWEEP_M]
+
+
+def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
+    k_blocks = -(-k // 64)
+    out: list[dict] = []
+    splits = [s for s in (2, 3, 4, 8, 16) if k_blocks >= 4 * s]
+    if m <= 128 and n >= 128:
+        widths = sorted({w for w in (16, 32, 64, 128) if w >= min(m, 128)} | {128})
+        for w in widths[:3]:
+            base = dict(tile_n=w, cta_group=1, swap_ab=1, group_m=1)
+            out.append(dict(base))
+            out.append(dict(base, stream_k=1))
+            for s in splits[:3]:
+                out.append(dict(base, split_k=s))
+    for tile_n in (64, 128, 256):
+        if tile_n > 64 and n < tile_n // 2:
+            continue
+        for cta_group in (1, 2):
+            if cta_group == 2 and m <= 128:
+                continue
+            base = dict(tile_n=tile_n, cta_group=cta_group, group_m=8)
+            out.append(dict(base))
+            out.append(dict(base, stream_k=1))
+            if tile_n >= 128:
+                out.append(dict(base, split_tail=2))
+            tiles = batch * -(-m // (128 * cta_group)) * -(-n // tile_n)
+            if tiles * cta_group <= 148:
+                for s in splits[:3]:
+                    out.append(dict(base, split_k=s))
+    return out
+
+
+def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: int = 5) -> dict:
+    dev = "cuda"
+    td = torch.bfloat16 if dtype == "bfloat16" else torch.float16
+    lead = (batch,) if op == "bmm" else ()
+    nbytes = 2.0 * batch * (m * k + n * k + m * n)
+    copies = _copies(nbytes, cap=12)
+    sets = []
+    for _ in range(copies):
+        a = torch.randn((*lead, m, k), device=dev, dtype=torch.float32).mul_(k ** -0.5).to(td)
+        bt = torch.randn((*lead, n, k), device=dev, dtype=torch.float32).to(td)
+        out = torch.empty((*lead, m, n), device=dev, dtype=td)
+        bias = torch.randn(n, device=dev).to(td) if op == "addmm" else None
+        sets.append((bias, a, bt, out))
+    flops = 2.0 * batch * m * n * k
+    est_ms = max(flops / 1.0e15, nbytes / 3e12) * 1e3 + 0.006
+    launches = int(max(4, min(30, 1.5 / est_ms)))
+    workspace = torch.zeros(16, dtype=torch.uint8, device=dev)
+    fns = {}
+    configs = {}
+    for i, cand in enumerate(candidates(op, batch, m, n, k)):
+        cfg = _lib.Config.from_dict(cand)
+        if not _lib.config_valid(cfg, op, dtype, batch, m, n, k):
+            continue
+        need = _lib.workspace_bytes(cfg, op, batch, m, n, k)
+        if need > MAX_WORKSPACE:
+            continue
+        if need > workspace.numel():
+            workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        configs[f"c{i}"] = cand
+
+    def make(cand):
+        cfg = _lib.Config.from_dict(cand)
+
+        def run(j, stream):
+            bias, a, bt, out = sets[j % copies]
+            _lib.gemm(op, dtype, bias.data_ptr() if bias is not None else 0, a.data_ptr(), bt.data_ptr(),
+                      out.data_ptr(), batch, m, n, k, cfg, workspace.data_ptr(), workspace.numel(), 0, stream)
+
+        return run
+
+    for name, cand in configs.items():
+        fns[name] = make(cand)
+
+    def cublas(j, stream):
+        bias, a, bt, out = sets[j % copies]
+        if op == "mm":
+            torch.mm(a, bt.t(), out=out)
+        elif op == "addmm":
+            torch.addmm(bias, a, bt.t(), out=out)
+        else:
+            torch.bmm(a, bt.transpose(1, 2), out=out)
+
+    fns["torch"] = cublas
+    times = time_interleaved(fns, launches, rounds)
+    torch_ms = times.pop("torch")
+    ranked = sorted(times.items(), key=lambda kv: kv[1])
+    results = [dict(config=configs[name], us=ms * 1e3, tflops=flops / ms / 1e9, gbs=nbytes / ms / 1e6,
+                    percentage_of_torch=100.0 * torch_ms / ms) for name, ms in ranked]
+    del sets
+    torch.cuda.empty_cache()
+    return dict(op=op, dtype=dtype, batch=batch, m=m, n=n, k=k, torch_us=torch_ms * 1e3, results=results)
+
+
+def measure(shapes, out_path: Path) -> None:
+    _lib.init(torch.cuda.current_device())
+    done = {}
+    if out_path.exists():
+        done = {tuple(r[key] for key in ("op", "dtype", "batch", "m", "n", "k")): r
+                for r in json.loads(out_path.read_text())}
+    for shape in shapes:
+        if tuple(shape) in done:
+            continue
+        row = tune_shape(*shape)
+        done[tuple(shape)] = row
+        best = row["results"][0]
+        print(f"[autotune] {shape}: best {best['us']:.1f} us {best['tflops']:.0f} TF/s {best['gbs']:.0f} GB/s "
+              f"({best['percentage_of_torch']:.0f}% of torch) {best['config']}", flush=True)
+        tmp = out_path.with_suffix(".tmp")
+        tmp.write_text(json.dumps(list(done.values()), indent=1))
+        os.replace(tmp, out_path)
+
+
+def emit_table(results_path: Path, table_path: Path, keep: int = 3) -> None:
+    rows = json.loads(results_path.read_text())
+    configs: list[dict] = []
+    index: dict[str, int] = {}
+    schedules: dict[tuple[str, str], dict[tuple[int, int, int, int], list[int]]] = {}
+    for row in rows:
+        picks = []
+        for res in row["results"][:keep]:
+            entry = dict(res["config"])
+            entry["us"] = round(res["us"], 2)
+            entry["tflops"] = round(res["tflops"], 1)
+            entry["percentage_of_torch"] = round(res["percentage_of_torch"], 1)
+            key = json.dumps(entry, sort_keys=True)
+            if key not in index:
+                index[key] = len(configs)
+                configs.append(entry)
+            picks.append(index[key])
+        schedules.setdefault((row["op"], row["dtype"]), {})[(row["batch"], row["m"], row["n"], row["k"])] = picks
+    lines = [
+        '"""Measured sm_100a GEMM schedules, keyed by the shapes they were measured on.',
+        "",
+        "Same two-level structure as the reference's table (ayla/gemm_schedule_table.py:14,",
+        ":1881): ``CONFIGS`` is a tuple of schedule dictionaries and",
+        "``SCHEDULES[(operation, dtype)][(batch, m, n, k)]`` lists indices into it, the",
+        "fastest measured schedule first.  The schedule keys are the fields of",
+        "``struct ayla_b200_config`` (``include/ayla_b200.h``); fields not listed take the",
+        "defaults in :mod:`ayla_b200.gemm_jit`.  ``us`` is the median CUDA-event time per launch",
+        "on a B200 (graph replay, operands rotating through more than 2.5x L2), ``tflops`` the",
+        "matching throughput and ``percentage_of_torch`` 100 x cuBLAS time / this time in the same",
+        "run; all three are informational and ignored by the launcher.",
+        "",
+        "Generated by ``python -m ayla_b200.autotune``; do not edit by hand.",
+        '"""',
+        "# fmt: off",
+        "CONFIGS: tuple[dict[str, object], ...] = (",
+    ]
+    for entry in configs:
+        body = ", ".join(f"{k}={v!r}" for k, v in entry.items())
+        lines.append(f"    dict({body}),")
+    lines.append(")")
+    lines.append("")
+    lines.append("SCHEDULES: dict[tuple[str, str], dict[tuple[int, int, int, int], tuple[int, ...]]] = {")
+    for (op, dtype), shapes in sorted(schedules.items()):
+        lines.append(f"    ({op!r}, {dtype!r}): {{")
+        for shape, picks in sorted(shapes.items()):
+            lines.append(f"        {shape!r}: {tuple(picks)!r},")
+        lines.append("    },")
+    lines.append("}")
+    lines.append("# fmt: on")
+    table_path.write_text("\n".join(lines) + "\n")
+    print(f"wrote {table_path}: {len(configs)} configs, {sum(len(v) for v in schedules.values())} shapes")
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--out", default="gpurun_out/autotune.json")
+    parser.add_argument("--shapes", default="all", choices=["all", "baseline", "sweep"])
+    parser.add_argument("--emit", default=None, help="write the schedule table to this path instead of measuring")
+    args = parser.parse_args()
+    out = Path(args.out)
+    if args.emit:
+        emit_table(out, Path(args.emit))
+        return
+    out.parent.mkdir(parents=True, exist_ok=True)
+    shapes = []
+    if args.shapes in ("all", "baseline"):
+        shapes += BASELINE_SHAPES
+    if args.shapes in ("all", "sweep"):
+        shapes += SWEEP_SHAPES
+    measure(shapes, out)
+
+
+if __name__ == "__main__":
+    main()

@@ -70,6 +70,7 @@ DeviceState g_devices[kMaxDevices];
 std::mutex g_init_mutex;
 PFN_cuTensorMapEncodeTiled g_encode_tiled = nullptr;
 std::atomic<long long> g_timeout_ns{2000000000ll};
+std::atomic<int> g_debug_flags{0};
 
 // ------------------------------------------------------------- tensor maps
 
@@ -149,6 +150,8 @@ struct Plan {
   int m_tiles, n_tiles, k_blocks, splits, kb_per_split, total_units, group_m, grid;
   int split_from_tile;  // first k-split tile (0 = all tiles split, == tiles when none is)
   int narrow_from_tile; // first tile done as two half-width units (== tiles when none is)
+  int stream_k, kb_per_cta;
+  long long slabs;      // fp32 partial-sum slabs of 128 x tile_n the schedule may write
   int row_tiles;  // 128-row x tile_n tiles (split-K counters, slabs)
 };
 
@@ -189,6 +192,12 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
   }
   if (c.split_tail < 0 || c.split_tail > 2) {
     return fail(AYLA_B200_E_UNSUPPORTED, "split_tail must be 0, 1 or 2");
+  }
+  if (c.stream_k != 0 && c.stream_k != 1) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "stream_k must be 0 or 1");
+  }
+  if (c.stream_k && (swiglu || c.split_k != 1 || c.split_tail != 0)) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "stream_k excludes split_k > 1, split_tail and the SwiGLU kernel");
   }
   if (c.split_tail == 2 && (swiglu || c.swap_ab || c.split_k != 1 || c.tile_n < 128)) {
     return fail(AYLA_B200_E_UNSUPPORTED,
@@ -252,6 +261,35 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
   } else if (grid < 1) {
     grid = 1;
   }
+  plan->stream_k = 0;
+  plan->kb_per_cta = 0;
+  if (c.stream_k) {
+    // Equal contiguous shares of the (tile, k-block) sequence; a share is never shorter
+    // than four k-blocks so that a segment is worth its epilogue.
+    const int64_t total_kb = tiles * plan->k_blocks;
+    if (total_kb > 0x7FFFFFFF) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "too much work for the stream-K schedule (%lld k-blocks)",
+                  (long long)total_kb);
+    }
+    int64_t ctas = grid / c.cta_group;
+    int64_t share = ceil_div(total_kb, ctas);
+    const int64_t min_share = plan->k_blocks < 4 ? plan->k_blocks : 4;
+    if (share < min_share) share = min_share;
+    ctas = ceil_div(total_kb, share);
+    plan->stream_k = 1;
+    plan->kb_per_cta = static_cast<int>(share);
+    plan->splits = 1;
+    plan->kb_per_split = plan->k_blocks;
+    plan->split_from_tile = static_cast<int>(tiles);
+    plan->narrow_from_tile = 0x7FFFFFFF;
+    plan->total_units = static_cast<int>(total_kb);
+    plan->row_tiles = static_cast<int>(ctas * c.cta_group);
+    // No tile is cut when every share is a whole number of tiles.
+    plan->slabs = (share % plan->k_blocks == 0) ? 0 : 2 * ctas * c.cta_group;
+    plan->group_m = c.group_m;
+    plan->grid = static_cast<int>(ctas * c.cta_group);
+    return AYLA_B200_OK;
+  }
   // Tiles processed at the same time by the persistent grid.
   const int64_t wave = grid / c.cta_group;
   int64_t split_from = 0;
@@ -284,6 +322,7 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
     return fail(AYLA_B200_E_UNSUPPORTED, "split_k with %d output tiles (limit %d); use split_k = 1",
                 plan->row_tiles, kMaxSplitKTiles);
   }
+  plan->slabs = (plan->splits > 1) ? static_cast<long long>(plan->row_tiles) * plan->splits : 0;
   plan->group_m = c.group_m;
   if (wave > units) grid = static_cast<int>(units * c.cta_group);
   plan->grid = grid;
@@ -291,14 +330,13 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
 }
 
 size_t counter_bytes_for(const Plan& p) {
-  if (p.splits <= 1) return 0;
+  if (p.slabs <= 0) return 0;
   return kCounterBytes;
 }
 
 size_t workspace_bytes_for(const Plan& p) {
-  if (p.splits <= 1) return 0;
-  return counter_bytes_for(p) +
-         static_cast<size_t>(p.row_tiles) * p.splits * 128 * p.kernel->tile_n * sizeof(float);
+  if (p.slabs <= 0) return 0;
+  return counter_bytes_for(p) + static_cast<size_t>(p.slabs) * 128 * p.kernel->tile_n * sizeof(float);
 }
 
 uint32_t make_idesc(int is_bf16, int mma_m, int mma_n) {
@@ -423,6 +461,8 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.kb_per_split = plan.kb_per_split;
   p.split_from_tile = plan.split_from_tile;
   p.narrow_from_tile = plan.narrow_from_tile;
+  p.stream_k = plan.stream_k;
+  p.kb_per_cta = plan.kb_per_cta;
   p.idesc_narrow = make_idesc(is_bf16, 128 * e.cta_group, e.tile_n / 2);
   p.total_units = plan.total_units;
   p.group_m = plan.group_m;
@@ -437,11 +477,12 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.out_batch_stride = out_rows * out_cols;
   p.status = status;
   p.timeout_ns = static_cast<unsigned long long>(g_timeout_ns.load());
-  if (plan.splits > 1) {
+  p.debug_flags = g_debug_flags.load();
+  if (plan.slabs > 0) {
     const size_t need = workspace_bytes_for(plan);
     if (workspace == nullptr || workspace_bytes < need) {
-      return fail(AYLA_B200_E_WORKSPACE, "split_k=%d needs a workspace of %zu bytes, got %zu",
-                  plan.splits, need, workspace == nullptr ? size_t(0) : workspace_bytes);
+      return fail(AYLA_B200_E_WORKSPACE, "this schedule (split_k=%d, stream_k=%d) needs a workspace of %zu bytes, got %zu",
+                  plan.splits, plan.stream_k, need, workspace == nullptr ? size_t(0) : workspace_bytes);
     }
     if (!aligned16(workspace)) {
       return fail(AYLA_B200_E_INVALID, "workspace must be 16-byte aligned");
@@ -771,6 +812,21 @@ void ayla_b200_set_wait_timeout_ms(int64_t ms) {
   if (ms < 1) ms = 1;
   g_timeout_ns.store(ms * 1000000ll);
 }
+
+int ayla_b200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                      size_t rows, void* stream) {
+  if (dst == nullptr || src == nullptr) return fail(AYLA_B200_E_INVALID, "dst and src must be non-null");
+  if (width_bytes == 0 || rows == 0) return AYLA_B200_OK;
+  if (dst_pitch < width_bytes || src_pitch < width_bytes) {
+    return fail(AYLA_B200_E_INVALID, "pitches must be at least the row width");
+  }
+  const cudaError_t err = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
+                                            cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail(AYLA_B200_E_CUDA, "cudaMemcpy2DAsync: %s", cudaGetErrorString(err));
+  return AYLA_B200_OK;
+}
+
+void ayla_b200_debug_set_flags(int flags) { g_debug_flags.store(flags); }
 
 const char* ayla_b200_last_error(void) { return g_last_error.c_str(); }
 

@@ -51,6 +51,8 @@ struct KernelParams {
   int kb_per_split;
   int split_from_tile;  // tiles with a linear index >= this are k-split; earlier tiles are whole
   int narrow_from_tile; // tiles >= this are done as two half-width units (no reduction needed)
+  int stream_k;         // 1: every CTA takes an equal, contiguous share of all (tile, k-block) work
+  int kb_per_cta;       // that share, in k-blocks
   uint32_t idesc_narrow; // instruction descriptor with N = BN / 2 for those units
   int total_units;    // batch * m_tiles * n_tiles * splits
   int group_m;        // raster: m-tiles per group
@@ -67,6 +69,7 @@ struct KernelParams {
   unsigned* status;   // optional device status word (may be null)
   unsigned long long timeout_ns;
   long long* trace;   // per-CTA cycle counters, written only by AYLA_B200_TRACE builds
+  int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
 };
 
 // Cycle accounting for tuning builds (-DAYLA_B200_TRACE): each role records the
@@ -160,36 +163,20 @@ struct BoundedWait {
 };
 
 struct WorkUnit {
-  int batch, m0, n0, kb0, kb1, split, row_tile;
+  int batch, m0, n0, kb0, kb1;
+  int nsplit;      // CTAs contributing to this tile (1 = this unit owns the whole K range)
+  int split;       // this unit's position among them (the order partials are summed in)
+  int counter;     // arrival counter of the tile
+  int slab0;       // static split: slab of contribution j is slab0 + j
+  int tile;        // linear tile index
   bool is_split;
   bool is_narrow;  // covers only OUT_BN / 2 columns starting at n0
 };
 
+// Linear tile index -> (batch, m0, n0) through the M-grouped raster.
 template <class T>
-__device__ __forceinline__ WorkUnit decode_unit(const KernelParams& p, int unit, int cta_rank) {
-  WorkUnit w;
-  // Units [0, split_from_tile) are whole tiles; the rest are (tile, k-split) pairs.
-  int tile, split;
-  int half = 0;
-  w.is_narrow = false;
-  if (unit >= p.narrow_from_tile) {
-    // Two half-width units per tile (never combined with k-splitting).
-    const int u = unit - p.narrow_from_tile;
-    tile = p.narrow_from_tile + (u >> 1);
-    half = u & 1;
-    split = 0;
-    w.is_split = false;
-    w.is_narrow = true;
-  } else if (unit < p.split_from_tile) {
-    tile = unit;
-    split = 0;
-    w.is_split = false;
-  } else {
-    const int u = unit - p.split_from_tile;
-    tile = p.split_from_tile + u / p.splits;
-    split = u - (u / p.splits) * p.splits;
-    w.is_split = p.splits > 1;
-  }
+__device__ __forceinline__ void locate_tile(const KernelParams& p, int tile, int half, int cta_rank,
+                                            WorkUnit& w) {
   const int tiles_per_batch = p.m_tiles * p.n_tiles;
   w.batch = tile / tiles_per_batch;
   const int t = tile - w.batch * tiles_per_batch;
@@ -202,18 +189,97 @@ __device__ __forceinline__ WorkUnit decode_unit(const KernelParams& p, int unit,
   const int n_t = r / rows_in_group;
   w.m0 = (m_t * T::CTA_GROUP + cta_rank) * T::BM;
   w.n0 = n_t * T::OUT_BN + half * (T::OUT_BN / 2);
-  w.split = split;
-  if (w.is_split) {
-    w.kb0 = split * p.kb_per_split;
-    w.kb1 = min(p.k_blocks, w.kb0 + p.kb_per_split);
-  } else {
-    w.kb0 = 0;
-    w.kb1 = p.k_blocks;
-  }
-  // Index of this CTA's 128-row tile among the split tiles (slabs and counters).
-  w.row_tile = (tile - p.split_from_tile) * T::CTA_GROUP + cta_rank;
-  return w;
+  w.tile = tile;
 }
+
+// The sequence of work units of one CTA (of one CTA pair when CTA_GROUP == 2).
+//  * static schedule: units cta, cta + G, cta + 2G, ... of a list of whole tiles,
+//    optionally followed by k-split tiles or half-width tiles;
+//  * stream-K schedule: the contiguous range [cta * kb_per_cta, (cta + 1) * kb_per_cta) of
+//    the (tile, k-block) sequence, cut at tile boundaries.  A tile cut between CTAs is
+//    finished by whichever contributor arrives last, summing in CTA order.
+template <class T>
+struct UnitCursor {
+  const KernelParams& p;
+  const int cta_rank;
+  const int cta, num_ctas;
+  int unit;      // static
+  int pos, end;  // stream-K, in k-blocks of the whole problem
+
+  __device__ UnitCursor(const KernelParams& p_, int cta_, int num_ctas_, int cta_rank_)
+      : p(p_), cta_rank(cta_rank_), cta(cta_), num_ctas(num_ctas_), unit(cta_) {
+    const long long total = static_cast<long long>(p.total_units);  // stream-K: total k-blocks
+    const long long b = static_cast<long long>(cta_) * p.kb_per_cta;
+    const long long e = b + p.kb_per_cta;
+    pos = static_cast<int>(b < total ? b : total);
+    end = static_cast<int>(e < total ? e : total);
+  }
+
+  __device__ __forceinline__ bool next(WorkUnit& w) {
+    if (p.stream_k) {
+      if (pos >= end) return false;
+      const int tile = pos / p.k_blocks;
+      const int tile_kb0 = tile * p.k_blocks;
+      locate_tile<T>(p, tile, 0, cta_rank, w);
+      w.is_narrow = false;
+      w.kb0 = pos - tile_kb0;
+      w.kb1 = min(p.k_blocks, end - tile_kb0);
+      pos = tile_kb0 + w.kb1;
+      const int first_cta = tile_kb0 / p.kb_per_cta;
+      const int last_cta = (tile_kb0 + p.k_blocks - 1) / p.kb_per_cta;
+      w.nsplit = last_cta - first_cta + 1;
+      w.split = cta - first_cta;
+      w.is_split = w.nsplit > 1;
+      w.counter = first_cta * T::CTA_GROUP + cta_rank;
+      w.slab0 = 0;
+      return true;
+    }
+    if (unit >= p.total_units) return false;
+    int tile, half = 0;
+    w.is_narrow = false;
+    w.is_split = false;
+    w.nsplit = 1;
+    w.split = 0;
+    if (unit >= p.narrow_from_tile) {
+      // Two half-width units per tile (never combined with k-splitting).
+      const int u = unit - p.narrow_from_tile;
+      tile = p.narrow_from_tile + (u >> 1);
+      half = u & 1;
+      w.is_narrow = true;
+    } else if (unit < p.split_from_tile) {
+      tile = unit;
+    } else {
+      const int u = unit - p.split_from_tile;
+      tile = p.split_from_tile + u / p.splits;
+      w.split = u - (u / p.splits) * p.splits;
+      w.nsplit = p.splits;
+      w.is_split = p.splits > 1;
+    }
+    locate_tile<T>(p, tile, half, cta_rank, w);
+    if (w.is_split) {
+      w.kb0 = w.split * p.kb_per_split;
+      w.kb1 = min(p.k_blocks, w.kb0 + p.kb_per_split);
+    } else {
+      w.kb0 = 0;
+      w.kb1 = p.k_blocks;
+    }
+    // Index of this CTA's 128-row tile among the split tiles (slabs and counters).
+    w.counter = (tile - p.split_from_tile) * T::CTA_GROUP + cta_rank;
+    w.slab0 = w.counter * p.splits;
+    unit += num_ctas;
+    return true;
+  }
+
+  // Slab that holds contribution j (0 <= j < nsplit) to the tile of unit w.
+  __device__ __forceinline__ int slab_of(const WorkUnit& w, int j) const {
+    if (!p.stream_k) return w.slab0 + j;
+    // Each CTA owns two slabs: one for the first segment of its range, one for its last.
+    const int first_cta = (w.tile * p.k_blocks) / p.kb_per_cta;
+    const int c = first_cta + j;
+    const int starts_in_tile = (c * p.kb_per_cta >= w.tile * p.k_blocks) ? 1 : 0;
+    return (2 * c + (starts_in_tile ? 0 : 1)) * T::CTA_GROUP + cta_rank;
+  }
+};
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
   if (is_bf16) {
@@ -323,16 +389,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // instructions.
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    const bool issuer = elect_one();
+    // With debug bit 0 set nothing is ever loaded: the MMA warp's wait for operands runs
+    // out and the launch ends with ST_TIMEOUT_FULL in the status word.
+    const bool issuer = elect_one() && (p.debug_flags & 1) == 0;
     const uint64_t pol_a = make_policy(p.l2_hint_a);
     const uint64_t pol_b = make_policy(p.l2_hint_b);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full_bar0 = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
     uint32_t stage = 0, phase = 0;
     AYLA_TRACE_BEGIN
-    for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
+    UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank);
+    WorkUnit w;
+    while (cursor.next(w)) {
       if (bw.aborted()) break;
-      const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
       // A narrow unit needs only the first half of each CTA's B slab; the full box is
       // still loaded (its tail is ignored by the narrower MMA).
       const int b_row = (T::EPI == EPI_SWIGLU)
@@ -375,9 +444,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       AYLA_TRACE_BEGIN
-      for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
+      UnitCursor<T> cursor(p, first_unit, unit_stride, 0);
+      WorkUnit w;
+      while (cursor.next(w)) {
         if (bw.aborted()) break;
-        const WorkUnit w = decode_unit<T>(p, unit, 0);
         AYLA_TRACE_WAIT(tr_wait2, bw.wait(bar_acc_empty + acc * 8, acc_phase ^ 1, ST_TIMEOUT_ACC_EMPTY))
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -443,8 +513,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // No early exit in this loop: the warps meet at named barriers, so after an abort
     // they keep walking the units together (every wait then returns at once) and the
     // results are garbage that the status word disowns.
-    for (int unit = first_unit; unit < p.total_units; unit += unit_stride) {
-      const WorkUnit w = decode_unit<T>(p, unit, cta_rank);
+    UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank);
+    WorkUnit w;
+    while (cursor.next(w)) {
       const bool split_k = w.is_split;
 
       if constexpr (T::EPI == EPI_BIAS && !T::TRANS_OUT) {
@@ -627,7 +698,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if constexpr (T::EPI != EPI_SWIGLU) {
           constexpr int STEP = T::TRANS_OUT ? 1 : 2;  // chunks handled back to back
           float4* slab = reinterpret_cast<float4*>(p.ws) +
-                         (static_cast<size_t>(w.row_tile) * p.splits + w.split) * (32 * BN);
+                         static_cast<size_t>(cursor.slab_of(w, w.split)) * (32 * BN);
 #pragma unroll 1
           for (int c0 = wsub * STEP; c0 < CHUNKS32; c0 += 2 * STEP) {
 #pragma unroll 1
@@ -659,17 +730,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           __threadfence();
           named_bar_sync(2, EPI_THREADS);
           if (epi_tid == 0) {
-            const unsigned old = atomicAdd(p.counters + w.row_tile, 1u);
-            const bool last = (old == static_cast<unsigned>(p.splits - 1));
-            if (last) p.counters[w.row_tile] = 0;  // leave the counter clean for the next launch
+            const unsigned old = atomicAdd(p.counters + w.counter, 1u);
+            const bool last = (old == static_cast<unsigned>(w.nsplit - 1));
+            if (last) p.counters[w.counter] = 0;  // leave the counter clean for the next launch
             *last_flag = last ? 1u : 0u;
           }
           named_bar_sync(2, EPI_THREADS);
           const bool last = *last_flag != 0;
           if (last) {
             __threadfence();
-            const float4* tile_slabs = reinterpret_cast<const float4*>(p.ws) +
-                                       static_cast<size_t>(w.row_tile) * p.splits * (32 * BN);
+            const float4* all_slabs = reinterpret_cast<const float4*>(p.ws);
 #pragma unroll 1
             for (int c0 = wsub * STEP; c0 < CHUNKS32; c0 += 2 * STEP) {
 #pragma unroll 1
@@ -677,8 +747,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-                for (int s = 0; s < p.splits; ++s) {
-                  const float4* sl = tile_slabs + static_cast<size_t>(s) * (32 * BN);
+                for (int s = 0; s < w.nsplit; ++s) {
+                  const float4* sl = all_slabs + static_cast<size_t>(cursor.slab_of(w, s)) * (32 * BN);
 #pragma unroll
                   for (int j = 0; j < CHUNK_COLS / 4; ++j) {
                     const float4 x = __ldcg(sl + (c32 * 8 + j) * 128 + row_in_tile);

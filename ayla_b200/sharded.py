@@ -60,6 +60,20 @@ def place_gathered_panel(out: torch.Tensor, gathered: torch.Tensor, panel: Panel
     view.copy_(gathered.permute(1, 0, 2))
 
 
+def place_gathered_panel_dma(out: torch.Tensor, gathered: torch.Tensor, panel: Panel, stream: int) -> None:
+    """Same placement as ``place_gathered_panel`` done by the copy engines: one strided 2-D copy
+    per source rank, so no SM is taken from the GEMM that runs meanwhile."""
+    from . import _lib
+
+    g, rows, width = gathered.shape
+    elt = out.element_size()
+    n = out.shape[1]
+    base = out.data_ptr() + panel.row0 * n * elt
+    for j in range(g):
+        _lib.copy_2d(base + j * width * elt, n * elt, gathered[j].data_ptr(), width * elt, width * elt, rows,
+                     stream)
+
+
 def bmm_sharded(a: torch.Tensor, bt: torch.Tensor, out: torch.Tensor, op) -> None:
     """Run ``op(a, bt, out)`` (a ``gemm_op('bmm', ...)``) on this rank's batch slice.
     The three tensors are this rank's local slices already."""
@@ -129,7 +143,7 @@ class NShardedMM:
                     pieces = [torch.empty_like(local) for _ in range(self.world)]
                     dist.all_gather(pieces, local.contiguous(), group=self.group)
                     gathered = torch.stack(pieces)
-                place_gathered_panel(out, gathered, panel)
+                place_gathered_panel_dma(out, gathered, panel, self.comm_stream.cuda_stream)
                 done = torch.cuda.Event()
                 done.record(self.comm_stream)
             done_events.append(done)

@@ -66,6 +66,9 @@ typedef struct ayla_b200_config {
   int32_t l2_hint_b;
   int32_t split_tail; /* wave quantisation: 1 = apply split_k only to the tiles of the last, partial
                          wave; 2 = do those tiles as two half-width units each (split_k must be 1) */
+  int32_t stream_k;   /* 1 = stream-K schedule: every CTA takes an equal contiguous share of all
+                         (tile, k-block) work; tiles cut between CTAs are reduced through the
+                         workspace.  Excludes split_k > 1 and split_tail. */
 } ayla_b200_config;
 
 /*
@@ -169,6 +172,15 @@ AYLA_B200_API size_t ayla_b200_workspace_bytes(const ayla_b200_config* cfg, int 
 AYLA_B200_API size_t ayla_b200_workspace_counter_bytes(const ayla_b200_config* cfg, int op, int64_t batch,
                                          int64_t m, int64_t n, int64_t k);
 
+/*
+ * Strided device-to-device copy on the copy engines (no SMs): `rows` rows of `width_bytes`,
+ * source rows `src_pitch` apart, destination rows `dst_pitch` apart.  Used by the N-sharded
+ * multi-GPU mm to put gathered column blocks of `out` in place while the GEMM of the next
+ * row panel owns the SMs.  The reference is single-GPU and has no counterpart.
+ */
+AYLA_B200_API int ayla_b200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                    size_t width_bytes, size_t rows, void* stream);
+
 /* Number of compiled kernel variants, and a description of variant i. */
 AYLA_B200_API int ayla_b200_kernel_count(void);
 AYLA_B200_API int ayla_b200_kernel_info(int i, int32_t* tile_n, int32_t* cta_group, int32_t* epilogue,
@@ -176,6 +188,14 @@ AYLA_B200_API int ayla_b200_kernel_info(int i, int32_t* tile_n, int32_t* cta_gro
 
 /* Bound, in milliseconds, on every device-side wait (default 2000). */
 AYLA_B200_API void ayla_b200_set_wait_timeout_ms(int64_t ms);
+
+/*
+ * Test hook for the failure path.  Bit 0: the TMA producer of every later launch issues no
+ * loads, so the MMA warp's bounded wait for operands runs out (after the wait timeout) and the
+ * launch ends normally with code 2 in `status` and garbage in `out`; the context stays usable.
+ * 0 restores normal operation.
+ */
+AYLA_B200_API void ayla_b200_debug_set_flags(int flags);
 
 AYLA_B200_API const char* ayla_b200_last_error(void);
 AYLA_B200_API const char* ayla_b200_version(void);

@@ -320,3 +320,67 @@ def test_abi_workspace_and_init_errors(device_state):
         _lib.gemm("mm", "bfloat16", 0, a.data_ptr(), a.data_ptr(), out.data_ptr(), 1, 256, 256, 1024, cfg,
                   0, 0, 0, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("m", [3, 128, 256])
+def test_dynamic_m_matmul(m):
+    """tests/gemm_collection/test_correctness.py:302-314 of the reference: m in {3, 128, 256},
+    n = 256, k = 64, seed = m; one cached schedule per shape."""
+    from ayla_b200.dynamic_m import make_dynamic_m_matmul
+
+    op = make_dynamic_m_matmul(256, 64, namespace=f"ayla_b200_dynamic_m_test_{m}")
+    g = torch.Generator().manual_seed(m)
+    lhs = torch.randn(m, 64, generator=g).bfloat16()
+    rhs = torch.randn(256, 64, generator=g).bfloat16()
+    out = op(lhs.to(DEV), rhs.to(DEV))
+    assert out.shape == (m, 256)
+    want = O.gemm_ref("mm", torch.bfloat16, lhs, rhs)
+    differing = int((out.cpu().view(torch.int16) != want.view(torch.int16)).sum())
+    assert differing <= max(1, out.numel() // 1000)
+
+
+# ------------------------------------------------------- failure detection (no GPU fault)
+
+@pytest.mark.parametrize("cfg", [dict(tile_n=128, cta_group=1), dict(tile_n=256, cta_group=2),
+                                 dict(tile_n=16, cta_group=1, swap_ab=1, group_m=1)])
+def test_bounded_wait_reports_a_stalled_pipeline_and_the_context_survives(cfg, device_state):
+    """A launch whose producer never delivers operands must not hang: the MMA warp's wait
+    runs out, the kernel finishes, the status word says which wait gave up (code 2 = waiting
+    for operands), and the next ordinary launch on the same context is correct."""
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(300, 264, generator=g).bfloat16()
+    bt = torch.randn(264, 264, generator=g).bfloat16()
+    try:
+        lib.ayla_b200_set_wait_timeout_ms(30)
+        lib.ayla_b200_debug_set_flags(1)
+        _, status = run_abi("mm", "bfloat16", (a, bt), cfg, device_state)
+        assert status & 0xFF in (2, 4), hex(status)   # the MMA wait (2) or, racing it, the epilogue's (4)
+    finally:
+        lib.ayla_b200_debug_set_flags(0)
+        lib.ayla_b200_set_wait_timeout_ms(2000)
+    device_state[1].zero_()
+    out, status = run_abi("mm", "bfloat16", (a, bt), cfg, device_state)
+    assert status == 0
+    assert_parity(out, O.mm_ref32(a, bt), "launch after a timed-out one")
+
+
+def test_launcher_check_status_raises_on_timeout():
+    lib = _lib.load()
+    compiler = gemm_jit_compiler("mm", "bfloat16")
+    a = torch.randn(256, 256, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(256, 256, device=DEV, dtype=torch.bfloat16)
+    compiler(a, a, out)
+    [launcher] = compiler._cache.values()
+    try:
+        lib.ayla_b200_set_wait_timeout_ms(30)
+        lib.ayla_b200_debug_set_flags(1)
+        compiler(a, a, out)
+        with pytest.raises(RuntimeError, match="timed out"):
+            launcher.check_status()
+    finally:
+        lib.ayla_b200_debug_set_flags(0)
+        lib.ayla_b200_set_wait_timeout_ms(2000)
+    compiler(a, a, out)
+    launcher.check_status()
+    torch.testing.assert_close(out, a @ a.T, atol=0.125, rtol=0.02)

@@ -44,3 +44,13 @@ def test_schema_rendering():
     assert make_schema("jit_mm_bf16", kinds) == "jit_mm_bf16(Tensor arg0, Tensor arg1, Tensor(a2!) arg2) -> ()"
     assert make_schema("f", [OperandKind.R, OperandKind.RESULT]) == "f(Tensor arg0) -> Tensor"
     assert make_schema("g", [OperandKind.RESULT, OperandKind.RESULT]) == "g() -> (Tensor, Tensor)"
+
+
+def test_dynamic_m_op_infers_its_result_on_meta():
+    from ayla_b200.dynamic_m import make_dynamic_m_matmul
+
+    op = make_dynamic_m_matmul(256, 64, namespace="ayla_b200_dynamic_m_meta_test")
+    lhs = torch.empty((3, 64), dtype=torch.bfloat16, device="meta")
+    rhs = torch.empty((256, 64), dtype=torch.bfloat16, device="meta")
+    out = op(lhs, rhs)
+    assert out.shape == (3, 256) and out.dtype == torch.bfloat16 and out.device.type == "meta"
