@@ -371,8 +371,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tmem_relinquish<CG>();
   }
   tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (CG == 2) {
+  if constexpr (CG == 1) {
+    // The producer warp needs only the barriers its own lane 0 has just initialised, so
+    // it announces them and starts loading at once; everyone else also waits for the
+    // TMEM allocation.
+    if (warp == 0) {
+      __syncwarp();
+      __threadfence_block();
+      named_bar_arrive(3, T::THREADS);
+    } else {
+      named_bar_sync(3, T::THREADS);
+    }
+  } else {
+    __syncthreads();
     // Both CTAs' barriers must exist before either one signals the other.
     cluster_arrive();
     cluster_wait();
