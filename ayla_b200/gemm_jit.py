@@ -115,9 +115,9 @@ def select_gemm_schedule(operation: str, dtype: str, m: int, n: int, k: int,
     """
     if min(batch, m, n, k) <= 0 or operation not in _OPERATIONS:
         return None
-    table = SCHEDULES.get((operation, dtype), {})
-    if not table:
+    if dtype not in _SHORT_DTYPES:
         return None
+    table = SCHEDULES.get((operation, dtype), {})
     if not _shape_supported(m, n, k, batch):
         return None
     query = (batch, m, n, k)
