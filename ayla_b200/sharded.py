@@ -15,6 +15,7 @@ Python so it can be tested on CPU ranks.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -83,19 +84,29 @@ def bmm_sharded(a: torch.Tensor, bt: torch.Tensor, out: torch.Tensor, op) -> Non
 class NShardedMM:
     """``out[M, N] = a[M, K] @ bt[N, K]^T`` with bt sharded by rows across the group.
 
-    Every rank ends up with the full ``out``.  ``panel_rows`` controls the overlap
-    granularity; ``reserve_sms`` leaves that many SMs free of GEMM CTAs so the
-    all-gather kernels of NCCL can run beside the GEMM.
+    Every rank ends up with the full ``out``.  Two ways to exchange the column blocks:
+
+    * ``exchange="nccl"`` (the default): every finished M-panel is all-gathered with NCCL on
+      a second stream as ``[g][rows][N/g]`` and put in place by strided DMA copies while the
+      GEMM of the next panel runs; ``reserve_sms`` SMs are left free of GEMM CTAs so NCCL's
+      kernels can run beside it.
+    * ``exchange="dma"``: ``out`` lives in symmetric memory and every rank pushes its finished
+      panel block straight into every peer's ``out`` with strided peer-to-peer copies on the
+      copy engines (plain stores over NVLink, no SMs, no staging, nothing to un-permute); one
+      barrier at the end.  Use ``runner.out`` as the output tensor.
     """
 
     def __init__(self, m: int, n: int, k: int, dtype: str, device: torch.device, group=None,
-                 panel_rows: int = 4096, reserve_sms: int = 8):
+                 panel_rows: int = 4096, reserve_sms: int = 16, exchange: str = "nccl"):
         from . import _lib
         from .gemm_jit import _TORCH_DTYPES, select_gemm_schedule
 
-        self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        if exchange not in ("nccl", "dma"):
+            raise ValueError(f"unknown exchange {exchange!r}")
+        self.exchange = exchange
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
         self.m, self.n, self.k, self.dtype = m, n, k, dtype
         self.col0, self.width = column_block(n, self.world, self.rank)
         self.panels = m_panels(m, panel_rows)
@@ -103,51 +114,81 @@ class NShardedMM:
         _lib.init(device.index)
         self._lib = _lib
         torch_dtype = _TORCH_DTYPES[dtype]
+        self.torch_dtype = torch_dtype
         rows = self.panels[0].rows
-        # double-buffered local panel and gather target
+        # double-buffered local panel (and gather target for the NCCL exchange)
         self.local = [torch.empty(rows, self.width, dtype=torch_dtype, device=device) for _ in range(2)]
-        self.gathered = [torch.empty(self.world, rows, self.width, dtype=torch_dtype, device=device)
-                         for _ in range(2)]
         seed = select_gemm_schedule("mm", dtype, rows, self.width, k)
         if seed is None:
             raise ValueError(f"no schedule for panel {rows}x{self.width}x{k}")
         cfg = dict(seed.builder_config)
         sms = torch.cuda.get_device_properties(device).multi_processor_count
-        if self.world > 1 and reserve_sms > 0:
-            cfg["grid_ctas"] = (sms - reserve_sms) & ~1
+        self.out = None
+        self.peer_out: list[torch.Tensor] = []
+        if exchange == "nccl":
+            self.gathered = [torch.empty(self.world, rows, self.width, dtype=torch_dtype, device=device)
+                             for _ in range(2)]
+            if self.world > 1 and reserve_sms > 0:
+                cfg["grid_ctas"] = (sms - reserve_sms) & ~1
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.out = symm_mem.empty((m, n), dtype=torch_dtype, device=device)
+            self._handle = symm_mem.rendezvous(self.out, self.group)
+            self.peer_out = [self._handle.get_buffer(r, (m, n), torch_dtype) for r in range(self.world)]
         self.cfg = _lib.Config.from_dict(cfg)
+        need = _lib.workspace_bytes(self.cfg, "mm", 1, rows, self.width, k)
+        self.workspace = torch.zeros(max(need, 16), dtype=torch.uint8, device=device)
         self.comm_stream = torch.cuda.Stream(device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
-    def __call__(self, a: torch.Tensor, bt_shard: torch.Tensor, out: torch.Tensor) -> None:
+    def __call__(self, a: torch.Tensor, bt_shard: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         lib = self._lib
+        if self.exchange == "dma":
+            out = self.out
+        elif out is None:
+            raise ValueError("the NCCL exchange needs an output tensor")
         main = torch.cuda.current_stream(self.device)
+        elt = out.element_size()
         done_events = []
         for i, panel in enumerate(self.panels):
             buf = i % 2
             if i >= 2:
-                # the gather that last read this local buffer must be finished
+                # the exchange that last read this local buffer must be finished
                 main.wait_event(done_events[i - 2])
             local = self.local[buf][:panel.rows]
             a_panel = a[panel.row0:panel.row0 + panel.rows]
             lib.gemm("mm", self.dtype, 0, a_panel.data_ptr(), bt_shard.data_ptr(), local.data_ptr(), 1,
-                     panel.rows, self.width, self.k, self.cfg, 0, 0, self.status.data_ptr(), main.cuda_stream)
+                     panel.rows, self.width, self.k, self.cfg, self.workspace.data_ptr(), self.workspace.numel(),
+                     self.status.data_ptr(), main.cuda_stream)
             ready = torch.cuda.Event()
             ready.record(main)
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
-                gathered = self.gathered[buf][:, :panel.rows]
-                if panel.rows == self.gathered[buf].shape[1]:
-                    dist.all_gather_into_tensor(gathered, local, group=self.group)
+                if self.exchange == "nccl":
+                    gathered = self.gathered[buf][:, :panel.rows]
+                    if panel.rows == self.gathered[buf].shape[1]:
+                        dist.all_gather_into_tensor(gathered, local, group=self.group)
+                    else:
+                        pieces = [torch.empty_like(local) for _ in range(self.world)]
+                        dist.all_gather(pieces, local.contiguous(), group=self.group)
+                        gathered = torch.stack(pieces)
+                    place_gathered_panel_dma(out, gathered, panel, self.comm_stream.cuda_stream)
                 else:
-                    pieces = [torch.empty_like(local) for _ in range(self.world)]
-                    dist.all_gather(pieces, local.contiguous(), group=self.group)
-                    gathered = torch.stack(pieces)
-                place_gathered_panel_dma(out, gathered, panel, self.comm_stream.cuda_stream)
+                    offset = (panel.row0 * self.n + self.col0) * elt
+                    for step in range(self.world):
+                        peer = (self.rank + step) % self.world
+                        lib.copy_2d(self.peer_out[peer].data_ptr() + offset, self.n * elt, local.data_ptr(),
+                                    self.width * elt, self.width * elt, panel.rows, self.comm_stream.cuda_stream)
                 done = torch.cuda.Event()
                 done.record(self.comm_stream)
             done_events.append(done)
+        if self.exchange == "dma":
+            with torch.cuda.stream(self.comm_stream):
+                # every rank's pushes must have landed before anyone reads its out
+                self._handle.barrier()
         main.wait_stream(self.comm_stream)
+        return out
 
 
 def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -> dict:
@@ -183,19 +224,36 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
                          "partition": f"batch 64 -> {count} per rank, no collective"}
         del a, bt, out
 
-    # ---- mm 32768^3, N-sharded + all-gather of out
-    big = 32768
-    try:
-        runner = NShardedMM(big, big, big, "bfloat16", device)
-        a = (torch.randn(big, big, device=device, dtype=torch.float32) * big ** -0.5).bfloat16()
-        bt = (torch.randn(runner.width, big, device=device, dtype=torch.float32) * big ** -0.5).bfloat16()
-        out = torch.empty(big, big, device=device, dtype=torch.bfloat16)
-        ms = timed(lambda: runner(a, bt, out), max(1, steps // 3))
-        results["mm32768"] = {"ms": ms, "tflops": 2.0 * big ** 3 / ms / 1e9,
-                              "partition": f"N -> {runner.width} columns per rank, all-gather of out in "
-                                           f"{len(runner.panels)} M-panels"}
-    except Exception as exc:  # noqa: BLE001 - reported, not fatal for the headline line
-        results["mm32768"] = {"error": f"{type(exc).__name__}: {exc}"}
+    # ---- mm 32768^3, N-sharded; identical seeded operands on every rank so a row panel of
+    # the assembled out can be checked against a single-GPU product of the full operands
+    big = int(os.environ.get("AYLA_B200_SHARDED_MM_SIZE", "32768"))
+    gen = torch.Generator(device=device).manual_seed(200)
+    a = torch.empty(big, big, device=device, dtype=torch.bfloat16)
+    bt_full = torch.empty(big, big, device=device, dtype=torch.bfloat16)
+    for t in (a, bt_full):
+        for r0 in range(0, big, 4096):
+            t[r0:r0 + 4096] = (torch.randn(4096, big, device=device, generator=gen) * big ** -0.5).bfloat16()
+    col0, width = column_block(big, world, rank)
+    bt = bt_full[col0:col0 + width].contiguous()
+    check_rows = slice(big // 2 - 128, big // 2 + 128)
+    want = torch.mm(a[check_rows], bt_full.t())
+    del bt_full
+    for exchange in ("nccl", "dma"):
+        key = "mm32768" if exchange == "nccl" else "mm32768_dma"
+        try:
+            runner = NShardedMM(big, big, big, "bfloat16", device, exchange=exchange)
+            out = runner.out if exchange == "dma" else torch.empty(big, big, device=device, dtype=torch.bfloat16)
+            out.zero_()
+            ms = timed(lambda: runner(a, bt, out), max(1, steps // 3))
+            err = (out[check_rows].float() - want.float()).norm() / want.float().norm()
+            results[key] = {"ms": ms, "tflops": 2.0 * big ** 3 / ms / 1e9, "fro_rel_vs_full_product": float(err),
+                            "status": int(runner.status.item()),
+                            "partition": f"N -> {runner.width} columns per rank, {exchange} exchange of out in "
+                                         f"{len(runner.panels)} M-panels"}
+            del runner, out
+        except Exception as exc:  # noqa: BLE001 - reported, not fatal for the headline line
+            results[key] = {"error": f"{type(exc).__name__}: {exc}"}
+        torch.cuda.empty_cache()
     return results if rank == 0 else {}
 
 

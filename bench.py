@@ -149,6 +149,8 @@ def dist_setup(n_gpus: int):
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # Keep NCCL's kernels small enough to run on the SMs the sharded GEMM leaves free.
+        os.environ.setdefault("NCCL_MAX_CTAS", "16")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
