@@ -193,6 +193,9 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
   if (c.split_tail < 0 || c.split_tail > 2) {
     return fail(AYLA_B200_E_UNSUPPORTED, "split_tail must be 0, 1 or 2");
   }
+  if (c.l2_prefetch < 0 || c.l2_prefetch > 256) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "l2_prefetch must be between 0 and 256 k-blocks");
+  }
   if (c.stream_k != 0 && c.stream_k != 1) {
     return fail(AYLA_B200_E_UNSUPPORTED, "stream_k must be 0 or 1");
   }
@@ -478,6 +481,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.status = status;
   p.timeout_ns = static_cast<unsigned long long>(g_timeout_ns.load());
   p.debug_flags = g_debug_flags.load();
+  p.l2_prefetch = c.l2_prefetch;
   if (plan.slabs > 0) {
     const size_t need = workspace_bytes_for(plan);
     if (workspace == nullptr || workspace_bytes < need) {
@@ -492,7 +496,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   }
 #ifdef AYLA_B200_TRACE
   // Tuning builds: without split-K the workspace receives the per-CTA cycle counters.
-  if (plan.splits <= 1 && workspace != nullptr && workspace_bytes >= static_cast<size_t>(plan.grid) * 128) {
+  if (plan.splits <= 1 && workspace != nullptr && workspace_bytes >= static_cast<size_t>(plan.grid) * 192) {
     p.trace = reinterpret_cast<long long*>(workspace);
   }
 #endif

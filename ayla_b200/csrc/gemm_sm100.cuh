@@ -70,6 +70,7 @@ struct KernelParams {
   unsigned long long timeout_ns;
   long long* trace;   // per-CTA cycle counters, written only by AYLA_B200_TRACE builds
   int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
+  int l2_prefetch;    // k-blocks the producer prefetches into L2 ahead of its shared-memory loads
 };
 
 // Cycle accounting for tuning builds (-DAYLA_B200_TRACE): each role records the
@@ -343,6 +344,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef AYLA_B200_TRACE
+  // Timeline of this CTA in globaltimer nanoseconds: entry, set-up done, first operands
+  // landed, last MMA committed, epilogue done, exit.
+  long long* stamps = (p.trace != nullptr) ? p.trace + gridDim.x * 16 + blockIdx.x * 8 : nullptr;
+  if (stamps != nullptr && threadIdx.x == 0) stamps[0] = static_cast<long long>(global_timer_ns());
+#endif
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
   const bool is_leader = cta_rank == 0;
 
@@ -390,6 +397,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef AYLA_B200_TRACE
+  if (stamps != nullptr && threadIdx.x == 32) stamps[1] = static_cast<long long>(global_timer_ns());
+#endif
 
   const int first_unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
   const int unit_stride = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
@@ -419,6 +429,17 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                             ? w.n0
                             : w.n0 + static_cast<int>(cta_rank) * (w.is_narrow ? T::B_ROWS / 2 : T::B_ROWS);
       const int b_batch = (T::EPI == EPI_SWIGLU) ? 0 : w.batch;
+      const CUtensorMap* tm_b_mine = &tm_b;
+      if constexpr (T::EPI == EPI_SWIGLU && CG == 2) tm_b_mine = is_leader ? &tm_b : &tm_b2;
+      auto prefetch_l2 = [&](int kb) {
+        tma_prefetch_l2_3d(&tm_a, kb * T::BK, w.m0, w.batch);
+        tma_prefetch_l2_3d(tm_b_mine, kb * T::BK, b_row, b_batch);
+        if constexpr (T::EPI == EPI_SWIGLU && CG == 1) tma_prefetch_l2_3d(&tm_b2, kb * T::BK, b_row, 0);
+      };
+      const int pf = p.l2_prefetch;
+      if (issuer && pf > 0) {
+        for (int kb = w.kb0; kb < w.kb1 && kb < w.kb0 + pf; ++kb) prefetch_l2(kb);
+      }
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
         if (issuer) {
@@ -431,12 +452,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             // Accumulator columns [0,128) = gate, [128,256) = up.
             tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, b_row, 0, pol_b);
             tma_load_3d<CG>(sb + T::B_BYTES / 2, &tm_b2, full_bar, kb * T::BK, b_row, 0, pol_b);
-          } else if constexpr (T::EPI == EPI_SWIGLU) {
-            // Pair: the leader's half of the B tile is gate, the peer's half is up.
-            tma_load_3d<CG>(sb, is_leader ? &tm_b : &tm_b2, full_bar, kb * T::BK, b_row, 0, pol_b);
           } else {
-            tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, b_row, b_batch, pol_b);
+            // Pair + SwiGLU: the leader's half of the B tile is gate, the peer's half is up.
+            tma_load_3d<CG>(sb, tm_b_mine, full_bar, kb * T::BK, b_row, b_batch, pol_b);
           }
+          if (pf > 0 && kb + pf < w.kb1) prefetch_l2(kb + pf);
         }
         if (++stage == STAGES) {
           stage = 0;
@@ -465,6 +485,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const uint32_t unit_idesc = w.is_narrow ? p.idesc_narrow : idesc;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL))
+#ifdef AYLA_B200_TRACE
+          if (stamps != nullptr && lane == 0 && stamps[2] == 0) stamps[2] = static_cast<long long>(global_timer_ns());
+#endif
           tc_fence_after_sync();
           if (issuer) {
             // Stage offset and the +32 bytes per 16-element K step, both in the
@@ -499,6 +522,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       }
       AYLA_TRACE_END(1)
+#ifdef AYLA_B200_TRACE
+      if (stamps != nullptr && lane == 0) stamps[3] = static_cast<long long>(global_timer_ns());
+#endif
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -758,15 +784,33 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-                for (int s = 0; s < w.nsplit; ++s) {
-                  const float4* sl = all_slabs + static_cast<size_t>(cursor.slab_of(w, s)) * (32 * BN);
+                // Two partials per round trip (both loads issued before either is summed);
+                // the order of the additions is still split 0, 1, 2, ...
+                for (int s = 0; s < w.nsplit; s += 2) {
+                  const bool two = s + 1 < w.nsplit;
+                  const float4* sl0 = all_slabs + static_cast<size_t>(cursor.slab_of(w, s)) * (32 * BN);
+                  const float4* sl1 =
+                      two ? all_slabs + static_cast<size_t>(cursor.slab_of(w, s + 1)) * (32 * BN) : sl0;
+                  float4 x0[CHUNK_COLS / 4], x1[CHUNK_COLS / 4];
+#pragma unroll
+                  for (int j = 0; j < CHUNK_COLS / 4; ++j) x0[j] = __ldcg(sl0 + (c32 * 8 + j) * 128 + row_in_tile);
+#pragma unroll
+                  for (int j = 0; j < CHUNK_COLS / 4; ++j) x1[j] = __ldcg(sl1 + (c32 * 8 + j) * 128 + row_in_tile);
 #pragma unroll
                   for (int j = 0; j < CHUNK_COLS / 4; ++j) {
-                    const float4 x = __ldcg(sl + (c32 * 8 + j) * 128 + row_in_tile);
-                    v[4 * j + 0] += x.x;
-                    v[4 * j + 1] += x.y;
-                    v[4 * j + 2] += x.z;
-                    v[4 * j + 3] += x.w;
+                    v[4 * j + 0] += x0[j].x;
+                    v[4 * j + 1] += x0[j].y;
+                    v[4 * j + 2] += x0[j].z;
+                    v[4 * j + 3] += x0[j].w;
+                  }
+                  if (two) {
+#pragma unroll
+                    for (int j = 0; j < CHUNK_COLS / 4; ++j) {
+                      v[4 * j + 0] += x1[j].x;
+                      v[4 * j + 1] += x1[j].y;
+                      v[4 * j + 2] += x1[j].z;
+                      v[4 * j + 3] += x1[j].w;
+                    }
                   }
                 }
                 const bool live = rows_live && (w.n0 + c32 * 32) < p.n;
@@ -792,6 +836,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
     if (warp == 2) {
       AYLA_TRACE_END(2)
+#ifdef AYLA_B200_TRACE
+      if (stamps != nullptr && lane == 0) stamps[4] = static_cast<long long>(global_timer_ns());
+#endif
     }
   }
 
@@ -813,6 +860,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, T::TMEM_COLS);
   }
+#ifdef AYLA_B200_TRACE
+  if (stamps != nullptr && threadIdx.x == 32) stamps[5] = static_cast<long long>(global_timer_ns());
+#endif
 #endif
 }
 

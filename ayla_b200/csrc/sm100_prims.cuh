@@ -127,6 +127,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm,
   }
 }
 
+// Ask the TMA unit to bring one box of the tensor into L2 (no shared memory, no
+// completion to wait for): lengthens the HBM request queue beyond what the shared
+// ring can hold.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* tm, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
 // Tiled 3-D store shared -> global (bulk async-group completion).
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, uint32_t src, int c0, int c1,
                                              int c2) {

@@ -66,6 +66,8 @@ typedef struct ayla_b200_config {
   int32_t l2_hint_b;
   int32_t split_tail; /* wave quantisation: 1 = apply split_k only to the tiles of the last, partial
                          wave; 2 = do those tiles as two half-width units each (split_k must be 1) */
+  int32_t l2_prefetch; /* k-blocks (of 64) the TMA producer prefetches into L2 ahead of its
+                          shared-memory loads; 0 = off.  Helps cold, short-K and streaming shapes. */
   int32_t stream_k;   /* 1 = stream-K schedule: every CTA takes an equal contiguous share of all
                          (tile, k-block) work; tiles cut between CTAs are reduced through the
                          workspace.  Excludes split_k > 1 and split_tail. */
