@@ -97,7 +97,7 @@ class NShardedMM:
     """
 
     def __init__(self, m: int, n: int, k: int, dtype: str, device: torch.device, group=None,
-                 panel_rows: int = 4096, reserve_sms: int = 16, exchange: str = "nccl"):
+                 panel_rows: int | None = None, reserve_sms: int = 16, exchange: str = "nccl"):
         from . import _lib
         from .gemm_jit import _TORCH_DTYPES, select_gemm_schedule
 
@@ -109,6 +109,10 @@ class NShardedMM:
         self.rank = dist.get_rank(self.group)
         self.m, self.n, self.k, self.dtype = m, n, k, dtype
         self.col0, self.width = column_block(n, self.world, self.rank)
+        if panel_rows is None:
+            # Four panels: each is several full waves of tiles (little wave quantisation) and
+            # only the last panel's exchange is left uncovered by compute.
+            panel_rows = max(2048, -(-m // 4))
         self.panels = m_panels(m, panel_rows)
         self.device = device
         _lib.init(device.index)
@@ -211,7 +215,20 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- bmm, batch 64 sharded; operands ~ the benchmark distributions
+    def timed_local(fn, reps):
+        """Single-GPU reference time on this rank (no collective inside)."""
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(reps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / reps
+
+    # ---- bmm, batch 64 sharded; operands ~ the benchmark distributions.  Rank 0 also runs the
+    # whole batch alone (the other ranks idle) as the single-GPU reference of the speed-up.
     op = gemm_op("bmm", "bfloat16")
     for name, (mm, nn, kk) in (("C3a", (2048, 2048, 128)), ("C3b", (2048, 128, 2048))):
         _, count = partition(64, world, rank)
@@ -223,6 +240,15 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
         results[name] = {"ms": ms, "tflops": flops / ms / 1e9, "gbs": 2.0 * 64 * (mm * kk + nn * kk + mm * nn) / ms / 1e6,
                          "partition": f"batch 64 -> {count} per rank, no collective"}
         del a, bt, out
+        if rank == 0:
+            a = torch.randn(64, mm, kk, device=device, dtype=torch.bfloat16)
+            bt = torch.randn(64, nn, kk, device=device, dtype=torch.bfloat16)
+            out = torch.empty(64, mm, nn, device=device, dtype=torch.bfloat16)
+            one = timed_local(lambda: op(a, bt, out), steps * 4)
+            results[name]["one_gpu_ms"] = one
+            results[name]["speedup_vs_one_gpu"] = one / ms
+            del a, bt, out
+        dist.barrier()
 
     # ---- mm 32768^3, N-sharded; identical seeded operands on every rank so a row panel of
     # the assembled out can be checked against a single-GPU product of the full operands
@@ -237,6 +263,13 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
     bt = bt_full[col0:col0 + width].contiguous()
     check_rows = slice(big // 2 - 128, big // 2 + 128)
     want = torch.mm(a[check_rows], bt_full.t())
+    one_gpu_ms = None
+    if rank == 0:
+        mm_op = gemm_op("mm", "bfloat16")
+        full_out = torch.empty(big, big, device=device, dtype=torch.bfloat16)
+        one_gpu_ms = timed_local(lambda: mm_op(a, bt_full, full_out), 2)
+        del full_out
+    dist.barrier()
     del bt_full
     for exchange in ("nccl", "dma"):
         key = "mm32768" if exchange == "nccl" else "mm32768_dma"
@@ -247,6 +280,8 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
             ms = timed(lambda: runner(a, bt, out), max(1, steps // 3))
             err = (out[check_rows].float() - want.float()).norm() / want.float().norm()
             results[key] = {"ms": ms, "tflops": 2.0 * big ** 3 / ms / 1e9, "fro_rel_vs_full_product": float(err),
+                            "one_gpu_ms": one_gpu_ms,
+                            "speedup_vs_one_gpu": (one_gpu_ms / ms) if one_gpu_ms else None,
                             "status": int(runner.status.item()),
                             "partition": f"N -> {runner.width} columns per rank, {exchange} exchange of out in "
                                          f"{len(runner.panels)} M-panels"}
