@@ -356,6 +356,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const BoundedWait bw{abort_flag, p.status, p.timeout_ns};
 
   if (threadIdx.x == 0) {
+    // Descriptor fetches first: they overlap the barrier set-up below.
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+    if constexpr (T::EPI == EPI_SWIGLU) prefetch_tensormap(&tm_b2);
+    if constexpr (!T::TRANS_OUT) prefetch_tensormap(&tm_d);
     *abort_flag = 0;
     *last_flag = 0;
     if ((smem_u32(smem) & 1023u) != 0) bw.give_up(ST_BAD_SMEM_ALIGN);
@@ -368,10 +373,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       mbar_init(bar_acc_empty + b * 8, T::EPI_WARPS * CG);
     }
     fence_mbar_init();
-    prefetch_tensormap(&tm_a);
-    prefetch_tensormap(&tm_b);
-    if constexpr (T::EPI == EPI_SWIGLU) prefetch_tensormap(&tm_b2);
-    if constexpr (!T::TRANS_OUT) prefetch_tensormap(&tm_d);
   }
   if (warp == 1) {
     tmem_alloc<CG>(smem_u32(tmem_slot), T::TMEM_COLS);

@@ -51,6 +51,20 @@ def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE) -
     )
 
 
+@cache
+def swiglu_fn_op(dtype: str, namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
+    """Functional form ``(x, w_gate, w_up) -> out`` of the fused SwiGLU op."""
+    from .swiglu import swiglu_compiler
+
+    return make_torch_custom_call(
+        swiglu_compiler(dtype),
+        [OperandKind.R] * 3 + [OperandKind.RESULT],
+        namespace=namespace,
+        name=f"swiglu_{_SHORT_DTYPES[dtype]}_fn",
+        infer_result_shapes=lambda x, w_gate, w_up: [(x.shape[0], w_gate.shape[0])],
+    )
+
+
 def _static_ints(values) -> tuple[int, ...] | None:
     out = []
     for v in values:
@@ -101,6 +115,109 @@ def _claim(operation: str, lhs, rhs, bias=None) -> tuple[str, tuple[int, ...]] |
     return dtype, (*batch, m, n, k)
 
 
+prims = torch.ops.prims
+
+
+def _strip_convert(node, dtype=None):
+    """The input of a ``convert_element_type`` node (to ``dtype`` if given), else the node."""
+    if (isinstance(node, torch.fx.Node) and node.op == "call_function"
+            and node.target is prims.convert_element_type.default
+            and (dtype is None or node.args[1] == dtype)):
+        return node.args[0]
+    return node
+
+
+def _silu_source(node):
+    """If ``node`` computes silu(g), return (g, nodes of the chain); else None.
+
+    Recognises ``aten.silu`` and the two forms Inductor's decompositions leave behind for
+    16-bit inputs: ``cvt16(div(cvt32(g), add(exp(neg(cvt32(g))), 1)))`` and
+    ``cvt16(mul(cvt32(g), sigmoid(cvt32(g))))``."""
+    if not isinstance(node, torch.fx.Node) or node.op != "call_function":
+        return None
+    if node.target is aten.silu.default:
+        return node.args[0], [node]
+    chain = [node]
+    inner = _strip_convert(node)
+    if inner is not node:
+        chain.append(inner)
+    if not isinstance(inner, torch.fx.Node) or inner.op != "call_function":
+        return None
+    if inner.target is aten.div.Tensor:
+        num, den = inner.args
+        if not (isinstance(den, torch.fx.Node) and den.target is aten.add.Tensor):
+            return None
+        exp, one = den.args[0], den.args[1]
+        if one != 1 or not (isinstance(exp, torch.fx.Node) and exp.target is aten.exp.default):
+            return None
+        neg = exp.args[0]
+        if not (isinstance(neg, torch.fx.Node) and neg.target is aten.neg.default):
+            return None
+        src_a, src_b = _strip_convert(num, torch.float32), _strip_convert(neg.args[0], torch.float32)
+        if src_a is not src_b:
+            return None
+        chain += [den, exp, neg] + [n for n in (num, neg.args[0]) if n is not src_a]
+        return src_a, chain
+    if inner.target is aten.mul.Tensor:
+        a, b = inner.args
+        for x, sig in ((a, b), (b, a)):
+            if isinstance(sig, torch.fx.Node) and sig.target is aten.sigmoid.default:
+                src_a, src_b = _strip_convert(x, torch.float32), _strip_convert(sig.args[0], torch.float32)
+                if src_a is src_b:
+                    chain += [sig] + [n for n in (x, sig.args[0]) if n is not src_a]
+                    return src_a, chain
+    return None
+
+
+def _only_used_by(node, allowed) -> bool:
+    return all(user in allowed for user in node.users)
+
+
+def route_swiglu(graph: torch.fx.Graph) -> int:
+    """Rewrite ``silu(x @ wg.T) * (x @ wu.T)`` (two claimed mm nodes on the same ``x``) into
+    one call of the fused SwiGLU op.  The reference only has the pieces of this fusion
+    (ayla/torch_compile.py:532-547 fuses a lone sigmoid; multi-source epilogues are a TODO,
+    ayla/passes/promote_buffers.py:626-628)."""
+    rewritten = 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target is not aten.mul.Tensor or len(node.args) != 2:
+            continue
+        for act, up in (node.args, node.args[::-1]):
+            found = _silu_source(act)
+            if found is None or not isinstance(up, torch.fx.Node):
+                continue
+            gate, chain = found
+            if not (isinstance(gate, torch.fx.Node) and gate.target is aten.mm.default
+                    and up.target is aten.mm.default and gate is not up):
+                continue
+            x, wg_t = gate.args
+            x2, wu_t = up.args
+            if x is not x2:
+                continue
+            claim_g, claim_u = _claim("mm", x, wg_t), _claim("mm", x, wu_t)
+            if claim_g is None or claim_u is None or claim_g != claim_u:
+                continue  # same dtype and the same (m, n, k), or it is not one SwiGLU
+            members = set(chain) | {node}
+            if not (_only_used_by(gate, members) and _only_used_by(up, {node})
+                    and all(_only_used_by(n, members) for n in chain)):
+                continue  # an intermediate is needed elsewhere: leave the graph alone
+            dtype = claim_g[0]
+            with graph.inserting_before(node):
+                wg = graph.call_function(aten.permute.default, (wg_t, [1, 0]))
+                wg.meta["val"] = _val(wg_t).permute(1, 0)
+                wu = graph.call_function(aten.permute.default, (wu_t, [1, 0]))
+                wu.meta["val"] = _val(wu_t).permute(1, 0)
+                new = graph.call_function(swiglu_fn_op(dtype), (x, wg, wu))
+                new.meta.update({k: v for k, v in node.meta.items() if k != "original_aten"})
+            node.replace_all_uses_with(new)
+            graph.erase_node(node)
+            rewritten += 1
+            break
+    if rewritten:
+        graph.eliminate_dead_code()
+    return rewritten
+
+
 def route_gemms(graph: torch.fx.Graph) -> int:
     """Rewrite every claimed ``aten.mm/addmm/bmm`` node of ``graph``; returns how many."""
     rewritten = 0
@@ -146,6 +263,7 @@ class AylaRoutingPass(CustomGraphPass):
         self.previous = previous
 
     def __call__(self, graph: torch.fx.Graph) -> None:
+        route_swiglu(graph)  # first: it consumes two mm nodes route_gemms would claim
         route_gemms(graph)
         if self.previous is not None:
             self.previous(graph)
@@ -167,6 +285,8 @@ def install() -> None:
         for dtype in _TORCH_DTYPES:
             gemm_op(operation, dtype)
             gemm_fn_op(operation, dtype)
+    for dtype in _TORCH_DTYPES:
+        swiglu_fn_op(dtype)
     current = inductor_config.post_grad_custom_post_pass
     if _installed is not None and current is _installed:
         return

@@ -73,6 +73,33 @@ def test_unsupported_gemms_are_declined(fn, specs):
     assert targets(gm) == before
 
 
+def test_swiglu_pattern_is_fused_and_partial_patterns_are_not():
+    import torch.nn.functional as F
+
+    specs = (((64, 32), BF16, "cuda"), ((48, 32), BF16, "cuda"), ((48, 32), BF16, "cuda"))
+    gm = trace(lambda x, wg, wu: F.silu(torch.mm(x, wg.t())) * torch.mm(x, wu.t()), *specs)
+    assert tc.route_swiglu(gm.graph) == 1
+    got = targets(gm)
+    assert torch.ops.ayla.swiglu_bf16_fn.default in got and aten.mm.default not in got
+    gm.graph.lint()
+    # operand order of the product does not matter
+    gm = trace(lambda x, wg, wu: torch.mm(x, wu.t()) * F.silu(torch.mm(x, wg.t())), *specs)
+    assert tc.route_swiglu(gm.graph) == 1
+    # the gate product is also returned: fusing would lose it, so the two mm are routed separately
+    gm = trace(lambda x, wg, wu: (F.silu(torch.mm(x, wg.t())) * torch.mm(x, wu.t()), torch.mm(x, wg.t())), *specs)
+    fused = tc.route_swiglu(gm.graph)
+    assert fused == 0 or aten.mm.default in targets(gm) or torch.ops.ayla.jit_mm_bf16_fn.default in targets(gm)
+    # different activations of x: not a SwiGLU
+    gm = trace(lambda x, y, wg: F.silu(torch.mm(x, wg.t())) * torch.mm(y, wg.t()),
+               ((64, 32), BF16, "cuda"), ((64, 32), BF16, "cuda"), ((48, 32), BF16, "cuda"))
+    assert tc.route_swiglu(gm.graph) == 0
+    # the whole pass: fused op, nothing left for route_gemms
+    gm = trace(lambda x, wg, wu: F.silu(torch.mm(x, wg.t())) * torch.mm(x, wu.t()), *specs)
+    tc.AylaRoutingPass()(gm.graph)
+    assert targets(gm).count(torch.ops.ayla.swiglu_bf16_fn.default) == 1
+    assert torch.ops.ayla.jit_mm_bf16_fn.default not in targets(gm)
+
+
 def test_install_is_idempotent_and_uninstall_restores():
     previous = inductor_config.post_grad_custom_post_pass
     try:
@@ -133,6 +160,26 @@ def test_torch_compile_routes_supported_gemms_to_jit(operation, dtype, ayla_inst
         expected = compute(a, bt, bias)
     torch.testing.assert_close(actual, expected, atol=0.125, rtol=0.02)
     assert any(f"jit_{operation}_" in source for source in code)
+
+
+@pytest.mark.gpu
+def test_torch_compile_fuses_swiglu(ayla_installed):
+    import torch.nn.functional as F
+    from torch._inductor.utils import run_and_get_code
+
+    x = torch.randn(200, 256, device="cuda", dtype=torch.bfloat16)
+    wg = (torch.randn(264, 256, device="cuda") * 256 ** -0.5).bfloat16()
+    wu = (torch.randn(264, 256, device="cuda") * 256 ** -0.5).bfloat16()
+
+    def mlp(x, wg, wu):
+        return F.silu(torch.mm(x, wg.T)) * torch.mm(x, wu.T)
+
+    with torch.no_grad(), inductor_config.patch(force_disable_caches=True):
+        actual, code = run_and_get_code(torch.compile(mlp, fullgraph=True, dynamic=False), x, wg, wu)
+    expected = (F.silu(x.float() @ wg.float().T) * (x.float() @ wu.float().T)).bfloat16()
+    torch.testing.assert_close(actual, expected, atol=0.05, rtol=0.02)
+    assert any("swiglu_bf16" in source for source in code)
+    assert not any("jit_mm_" in source for source in code)
 
 
 @pytest.mark.gpu
