@@ -394,36 +394,45 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
     c->group_m = 1;
     return;
   }
-  // Widest tile that still gives every SM work; pair CTAs when the tile count allows.
-  const int widths[3] = {256, 128, 64};
-  int tile_n = 64;
-  for (int i = 0; i < 3; ++i) {
-    const int w = widths[i];
-    if (n < w && w > 64) continue;
-    const int64_t tiles = batch * ceil_div(m, 128) * ceil_div(n, w);
-    if (tiles >= sm_count || w == 64) {
-      tile_n = w;
-      break;
+  // Row-major form: pick (tile width, CTA pairing, k-split) by a small cost model fitted to
+  // the B200 sweep.  Costs are in units of "one 64-deep k-block of a paired 256-wide tile at
+  // full tensor rate" (about 0.28 us): a tile costs its width over the measured efficiency of
+  // its shape, waves are whole, a k-split pays a fixed fix-up and every launch a fixed
+  // prologue/epilogue that grows with the tile width.
+  struct Shape { int tile_n, cta_group; double eff; };
+  static const Shape kShapes[6] = {{256, 2, 1.00}, {256, 1, 0.88}, {128, 2, 0.80},
+                                   {128, 1, 0.62}, {64, 2, 0.50}, {64, 1, 0.40}};
+  double best_cost = 1e300;
+  for (const Shape& sh : kShapes) {
+    if (sh.cta_group == 2 && (m <= 128 || k_blocks <= 4)) continue;  // shallow K: pairing only adds set-up
+    if (sh.tile_n > 64 && n * 2 <= sh.tile_n) continue;
+    const int64_t ctas = sm_count / sh.cta_group;
+    const int64_t tiles = batch * ceil_div(m, 128 * sh.cta_group) * ceil_div(n, sh.tile_n);
+    const double tile_cost = (sh.tile_n / 256.0) / sh.eff * static_cast<double>(k_blocks);
+    const double launch_cost = 6.0 + sh.tile_n / 64.0;
+    for (int split = 1; split <= 16; split *= 2) {
+      if (split > 1 && (k_blocks < 8 * split || tiles * split > ctas)) break;
+      const int64_t units = tiles * split;
+      double waves = static_cast<double>(ceil_div(units, ctas));
+      int tail = 0;
+      if (split == 1 && units > ctas && sh.tile_n >= 128) {
+        const int64_t rest = units % ctas;
+        if (rest != 0 && rest * 2 <= ctas) {
+          waves -= 0.45;  // the thin last wave runs at half width
+          tail = 2;
+        }
+      }
+      // The last arriver sums `split` partial tiles one after the other.
+      const double fixup = split > 1 ? 4.0 + 0.9 * split * (sh.tile_n / 64.0) : 0.0;
+      const double cost = waves * tile_cost / split + fixup + launch_cost;
+      if (cost < best_cost) {
+        best_cost = cost;
+        c->tile_n = sh.tile_n;
+        c->cta_group = sh.cta_group;
+        c->split_k = split;
+        c->split_tail = tail;
+      }
     }
-  }
-  c->tile_n = tile_n;
-  int64_t tiles = batch * ceil_div(m, 128) * ceil_div(n, tile_n);
-  if (m >= 256 && tiles >= static_cast<int64_t>(sm_count)) {
-    c->cta_group = 2;
-    tiles = batch * ceil_div(m, 256) * ceil_div(n, tile_n);
-  }
-  const int64_t wave = sm_count / c->cta_group;
-  const int64_t rest = tiles % wave;
-  if (tiles > wave && rest != 0 && rest * 2 <= wave && tile_n >= 128) {
-    // More than one wave with a thin last wave: do those tiles as half-width units so
-    // the last wave keeps every SM busy.
-    c->split_tail = 2;
-  } else if (tiles * 2 <= sm_count && k_blocks >= 16) {
-    int64_t s = sm_count / tiles;
-    const int64_t max_s = k_blocks / 8;
-    if (s > max_s) s = max_s;
-    if (s < 1) s = 1;
-    c->split_k = static_cast<int32_t>(s);
   }
 }
 
@@ -496,7 +505,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   }
 #ifdef AYLA_B200_TRACE
   // Tuning builds: without split-K the workspace receives the per-CTA cycle counters.
-  if (plan.splits <= 1 && workspace != nullptr && workspace_bytes >= static_cast<size_t>(plan.grid) * 192) {
+  if (plan.splits <= 1 && workspace != nullptr && workspace_bytes >= (4096 + static_cast<size_t>(plan.grid) * 8) * 8) {
     p.trace = reinterpret_cast<long long*>(workspace);
   }
 #endif

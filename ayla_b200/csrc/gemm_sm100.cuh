@@ -347,7 +347,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #ifdef AYLA_B200_TRACE
   // Timeline of this CTA in globaltimer nanoseconds: entry, set-up done, first operands
   // landed, last MMA committed, epilogue done, exit.
-  long long* stamps = (p.trace != nullptr) ? p.trace + gridDim.x * 16 + blockIdx.x * 8 : nullptr;
+  long long* stamps = (p.trace != nullptr) ? p.trace + 4096 + blockIdx.x * 8 : nullptr;
   if (stamps != nullptr && threadIdx.x == 0) stamps[0] = static_cast<long long>(global_timer_ns());
 #endif
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
@@ -832,8 +832,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     }
     if constexpr (!T::TRANS_OUT) {
-      // Shared memory must outlive the bulk stores that read it.
-      if (lane == 0) tma_store_wait_all<0>();
+      // Shared memory must outlive the bulk stores that read it; their global writes are
+      // complete, like every other store of the grid, when the grid is.
+      if (lane == 0) tma_store_wait_read<0>();
     }
     if (warp == 2) {
       AYLA_TRACE_END(2)
