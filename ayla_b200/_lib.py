@@ -52,6 +52,7 @@ class Config(ctypes.Structure):
         ("l2_hint_b", ctypes.c_int32),
         ("split_tail", ctypes.c_int32),
         ("l2_prefetch", ctypes.c_int32),
+        ("cluster_split", ctypes.c_int32),
         ("stream_k", ctypes.c_int32),
     ]
 
@@ -60,7 +61,7 @@ class Config(ctypes.Structure):
     @classmethod
     def from_dict(cls, values: dict) -> "Config":
         cfg = cls(tile_n=256, cta_group=1, swap_ab=0, split_k=1, group_m=8, grid_ctas=0,
-                  l2_hint_a=0, l2_hint_b=0, split_tail=0, l2_prefetch=0, stream_k=0)
+                  l2_hint_a=0, l2_hint_b=0, split_tail=0, l2_prefetch=0, cluster_split=0, stream_k=0)
         for key in cls.FIELDS:
             if key in values and values[key] is not None:
                 setattr(cfg, key, int(values[key]))

@@ -53,6 +53,9 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
             out.append(dict(base, stream_k=1))
             for s in splits[:3]:
                 out.append(dict(base, split_k=s))
+            for s in (2, 4, 8):
+                if k_blocks >= 4 * s and w % (4 * s) == 0:
+                    out.append(dict(base, split_k=s, cluster_split=1))
     for tile_n in (64, 128, 256):
         if tile_n > 64 and n < tile_n // 2:
             continue
@@ -68,6 +71,10 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
             if tiles * cta_group <= 148:
                 for s in splits[:3]:
                     out.append(dict(base, split_k=s))
+                if cta_group == 1:
+                    for s in (2, 4, 8):
+                        if k_blocks >= 4 * s and tiles * s <= 296:
+                            out.append(dict(base, split_k=s, cluster_split=1))
     return out
 
 

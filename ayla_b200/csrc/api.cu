@@ -151,6 +151,7 @@ struct Plan {
   int split_from_tile;  // first k-split tile (0 = all tiles split, == tiles when none is)
   int narrow_from_tile; // first tile done as two half-width units (== tiles when none is)
   int stream_k, kb_per_cta;
+  int cluster_split;    // cluster size of the cluster split-K schedule (0 = not used)
   long long slabs;      // fp32 partial-sum slabs of 128 x tile_n the schedule may write
   int row_tiles;  // 128-row x tile_n tiles (split-K counters, slabs)
 };
@@ -192,6 +193,21 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
   }
   if (c.split_tail < 0 || c.split_tail > 2) {
     return fail(AYLA_B200_E_UNSUPPORTED, "split_tail must be 0, 1 or 2");
+  }
+  if (c.cluster_split != 0 && c.cluster_split != 1) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split must be 0 or 1");
+  }
+  if (c.cluster_split) {
+    if (swiglu || c.cta_group != 1 || c.stream_k || c.split_tail) {
+      return fail(AYLA_B200_E_UNSUPPORTED,
+                  "cluster_split needs cta_group = 1 and excludes stream_k, split_tail and the SwiGLU kernel");
+    }
+    if (c.split_k != 2 && c.split_k != 4 && c.split_k != 8) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split needs split_k in {2, 4, 8} (the cluster size)");
+    }
+    if (c.tile_n % (4 * c.split_k) != 0) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split needs tile_n to be a multiple of 4 * split_k");
+    }
   }
   if (c.l2_prefetch < 0 || c.l2_prefetch > 256) {
     return fail(AYLA_B200_E_UNSUPPORTED, "l2_prefetch must be between 0 and 256 k-blocks");
@@ -291,6 +307,29 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
     plan->slabs = (share % plan->k_blocks == 0) ? 0 : 2 * ctas * c.cta_group;
     plan->group_m = c.group_m;
     plan->grid = static_cast<int>(ctas * c.cta_group);
+    return AYLA_B200_OK;
+  }
+  plan->cluster_split = 0;
+  if (c.cluster_split) {
+    // One cluster of split_k CTAs per tile, one tile per cluster; every CTA must have a
+    // non-empty share of K.
+    const int s_k = c.split_k;
+    const int per = static_cast<int>(ceil_div(plan->k_blocks, s_k));
+    if (static_cast<int64_t>(s_k - 1) * per >= plan->k_blocks) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split: %d k-blocks cannot be shared by %d CTAs",
+                  plan->k_blocks, s_k);
+    }
+    if (tiles * s_k > 0x7FFFFFFF) return fail(AYLA_B200_E_UNSUPPORTED, "too many tiles (%lld)", (long long)tiles);
+    plan->cluster_split = s_k;
+    plan->splits = s_k;
+    plan->kb_per_split = per;
+    plan->split_from_tile = 0;
+    plan->narrow_from_tile = 0x7FFFFFFF;
+    plan->total_units = static_cast<int>(tiles);
+    plan->row_tiles = 0;
+    plan->slabs = 0;
+    plan->group_m = c.group_m;
+    plan->grid = static_cast<int>(tiles * s_k);
     return AYLA_B200_OK;
   }
   // Tiles processed at the same time by the persistent grid.
@@ -473,6 +512,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.kb_per_split = plan.kb_per_split;
   p.split_from_tile = plan.split_from_tile;
   p.narrow_from_tile = plan.narrow_from_tile;
+  p.cluster_split = plan.cluster_split;
   p.stream_k = plan.stream_k;
   p.kb_per_cta = plan.kb_per_cta;
   p.idesc_narrow = make_idesc(is_bf16, 128 * e.cta_group, e.tile_n / 2);
@@ -510,6 +550,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   }
 #endif
   la.grid = plan.grid;
+  la.cluster_x = plan.cluster_split;
   la.stream = stream;
   const cudaError_t err = e.launch(la);
   if (err != cudaSuccess) {

@@ -51,6 +51,8 @@ struct KernelParams {
   int kb_per_split;
   int split_from_tile;  // tiles with a linear index >= this are k-split; earlier tiles are whole
   int narrow_from_tile; // tiles >= this are done as two half-width units (no reduction needed)
+  int cluster_split;    // S > 0: the S k-splits of a tile are the CTAs of one cluster and are
+                        // summed through distributed shared memory (one tile per cluster)
   int stream_k;         // 1: every CTA takes an equal, contiguous share of all (tile, k-block) work
   int kb_per_cta;       // that share, in k-blocks
   uint32_t idesc_narrow; // instruction descriptor with N = BN / 2 for those units
@@ -204,11 +206,12 @@ struct UnitCursor {
   const KernelParams& p;
   const int cta_rank;
   const int cta, num_ctas;
+  const int split_rank;  // cluster split-K: this CTA's k-split
   int unit;      // static
   int pos, end;  // stream-K, in k-blocks of the whole problem
 
-  __device__ UnitCursor(const KernelParams& p_, int cta_, int num_ctas_, int cta_rank_)
-      : p(p_), cta_rank(cta_rank_), cta(cta_), num_ctas(num_ctas_), unit(cta_) {
+  __device__ UnitCursor(const KernelParams& p_, int cta_, int num_ctas_, int cta_rank_, int split_rank_ = 0)
+      : p(p_), cta_rank(cta_rank_), cta(cta_), num_ctas(num_ctas_), split_rank(split_rank_), unit(cta_) {
     const long long total = static_cast<long long>(p.total_units);  // stream-K: total k-blocks
     const long long b = static_cast<long long>(cta_) * p.kb_per_cta;
     const long long e = b + p.kb_per_cta;
@@ -241,7 +244,13 @@ struct UnitCursor {
     w.is_split = false;
     w.nsplit = 1;
     w.split = 0;
-    if (unit >= p.narrow_from_tile) {
+    if (p.cluster_split > 0) {
+      // One tile per cluster; this CTA's share of K is its rank in the cluster.
+      tile = unit;
+      w.split = split_rank;
+      w.nsplit = p.cluster_split;
+      w.is_split = true;
+    } else if (unit >= p.narrow_from_tile) {
       // Two half-width units per tile (never combined with k-splitting).
       const int u = unit - p.narrow_from_tile;
       tile = p.narrow_from_tile + (u >> 1);
@@ -402,8 +411,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (stamps != nullptr && threadIdx.x == 32) stamps[1] = static_cast<long long>(global_timer_ns());
 #endif
 
-  const int first_unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
-  const int unit_stride = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
+  // Cluster split-K (single-CTA tiles only): cluster size, and this CTA's rank in it.
+  const int csk = (CG == 1) ? p.cluster_split : 0;
+  const int csk_rank = csk > 0 ? static_cast<int>(cluster_ctarank()) : 0;
+  const int first_unit = (CG == 2) ? (blockIdx.x >> 1) : (csk > 0 ? blockIdx.x / csk : blockIdx.x);
+  const int unit_stride = (CG == 2) ? (gridDim.x >> 1) : (csk > 0 ? gridDim.x / csk : gridDim.x);
 
   // The producer and MMA warps run their loops with all 32 lanes (addresses,
   // coordinates and descriptors are warp-uniform, which lets the compiler keep them
@@ -420,7 +432,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t full_bar0 = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
     uint32_t stage = 0, phase = 0;
     AYLA_TRACE_BEGIN
-    UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank);
+    UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank, csk_rank);
     WorkUnit w;
     while (cursor.next(w)) {
       if (bw.aborted()) break;
@@ -466,6 +478,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     }
     AYLA_TRACE_END(0)
+    if (csk > 0) {
+      // Cluster barriers count every thread of the cluster: keep step with the two the
+      // epilogue warps use around the exchange of partial tiles.
+      cluster_arrive();
+      cluster_wait();
+      cluster_arrive();
+      cluster_wait();
+    }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (is_leader) {
@@ -476,7 +496,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       AYLA_TRACE_BEGIN
-      UnitCursor<T> cursor(p, first_unit, unit_stride, 0);
+      UnitCursor<T> cursor(p, first_unit, unit_stride, 0, csk_rank);
       WorkUnit w;
       while (cursor.next(w)) {
         if (bw.aborted()) break;
@@ -527,6 +547,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (stamps != nullptr && lane == 0) stamps[3] = static_cast<long long>(global_timer_ns());
 #endif
     }
+    if (csk > 0) {
+      cluster_arrive();
+      cluster_wait();
+      cluster_arrive();
+      cluster_wait();
+    }
   } else {
     // ---------------------------------------------------------------- epilogue
     // Eight warps: warp w may read TMEM lanes [32 * (w % 4), +32), so two warps share
@@ -551,7 +577,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // No early exit in this loop: the warps meet at named barriers, so after an abort
     // they keep walking the units together (every wait then returns at once) and the
     // results are garbage that the status word disowns.
-    UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank);
+    UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank, csk_rank);
     WorkUnit w;
     while (cursor.next(w)) {
       const bool split_k = w.is_split;
@@ -657,7 +683,83 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       };
 
-      if (!split_k) {
+      if (csk > 0) {
+        // ---- cluster split-K: the S CTAs of the cluster hold the S partial sums of this
+        // tile.  Each CTA owns BN / S columns of it: every CTA sends each owner its partial
+        // of the owner's columns through distributed shared memory (into the operand ring,
+        // idle by now), then each owner adds the S partials in rank order and stores.
+        if constexpr (CG == 1 && T::EPI != EPI_SWIGLU) {
+          const int slice_cols = BN / csk;
+          const int slice_shift = __ffs(slice_cols) - 1;
+          const int slice_c4 = slice_cols >> 2;
+          const uint32_t exch = smem_u32(smem);
+          cluster_arrive();  // every CTA's MMAs are done: no ring is being read any more
+          cluster_wait();
+          constexpr int STEP = T::TRANS_OUT ? 1 : 2;
+#pragma unroll 1
+          for (int c0 = wsub * STEP; c0 < CHUNKS32; c0 += 2 * STEP) {
+#pragma unroll 1
+            for (int c32 = c0; c32 < c0 + STEP && c32 < CHUNKS32; ++c32) {
+              uint32_t r[32];
+              if constexpr (CHUNK_COLS == 32) {
+                tmem_ld_32x32(t_acc + c32 * 32, r);
+              } else {
+                tmem_ld_32x16(t_acc, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
+              }
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < CHUNK_COLS / 4; ++j) {
+                const int col = c32 * 32 + 4 * j;
+                const int owner = col >> slice_shift;
+                const int c4 = (col - (owner << slice_shift)) >> 2;
+                const uint32_t dst =
+                    map_to_cta(exch + ((csk_rank * slice_c4 + c4) * 128 + row_in_tile) * 16, owner);
+                st_cluster_v4(dst, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                              __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              }
+            }
+          }
+          release_accumulator();
+          cluster_arrive();  // all partials delivered
+          cluster_wait();
+          const int row = w.m0 + row_in_tile;
+          if (row < p.m) {
+            uint8_t* base = reinterpret_cast<uint8_t*>(p.out) + 2 * (w.batch * p.out_batch_stride);
+            const float4* mine = reinterpret_cast<const float4*>(smem);
+            for (int c4 = wsub; c4 < slice_c4; c4 += 2) {
+              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int s = 0; s < csk; ++s) {
+                const float4 x = mine[(s * slice_c4 + c4) * 128 + row_in_tile];
+                sum.x += x.x;
+                sum.y += x.y;
+                sum.z += x.z;
+                sum.w += x.w;
+              }
+              const int col = w.n0 + csk_rank * slice_cols + c4 * 4;
+              if (col < p.n) {
+                float v4[4] = {sum.x, sum.y, sum.z, sum.w};
+                if constexpr (T::TRANS_OUT) {
+                  float bias_v = 0.0f;
+                  if constexpr (T::EPI == EPI_BIAS) bias_v = load_elem(p.bias, row, is_bf16);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (col + j < p.n) store_elem(base, (col + j) * p.out_ld + row, v4[j] + bias_v, is_bf16);
+                  }
+                } else {
+                  if constexpr (T::EPI == EPI_BIAS) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v4[j] += load_elem(p.bias, col + j, is_bf16);
+                  }
+                  uint2 pk;
+                  pk.x = pack2(v4[0], v4[1], is_bf16);
+                  pk.y = pack2(v4[2], v4[3], is_bf16);
+                  *reinterpret_cast<uint2*>(base + 2 * (static_cast<long long>(row) * p.out_ld + col)) = pk;
+                }
+              }
+            }
+          }
+        }
+      } else if (!split_k) {
         if constexpr (!T::TRANS_OUT) {
           // This warp's 64-column groups, software-pipelined over 32-column chunks: the
           // TMEM load of the next chunk is in flight while this one is converted,

@@ -13,6 +13,7 @@ struct LaunchArgs {
   CUtensorMap tm_a, tm_b, tm_b2, tm_d;
   KernelParams p;
   int grid;
+  int cluster_x;  // 0 = the variant's own cluster width (1 or 2)
   cudaStream_t stream;
 };
 
@@ -45,9 +46,10 @@ cudaError_t launch_variant(const LaunchArgs& a) {
   cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
   cfg.numAttrs = 0;
-  if (T::CTA_GROUP == 2) {
+  const int cluster_x = (T::CTA_GROUP == 2) ? 2 : a.cluster_x;
+  if (cluster_x > 1) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster_x);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;

@@ -46,6 +46,7 @@ _DEFAULTS: dict[str, object] = {
     "l2_hint_b": 0,
     "split_tail": 0,
     "l2_prefetch": 0,
+    "cluster_split": 0,
     "stream_k": 0,
 }
 

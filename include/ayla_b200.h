@@ -68,6 +68,9 @@ typedef struct ayla_b200_config {
                          wave; 2 = do those tiles as two half-width units each (split_k must be 1) */
   int32_t l2_prefetch; /* k-blocks (of 64) the TMA producer prefetches into L2 ahead of its
                           shared-memory loads; 0 = off.  Helps cold, short-K and streaming shapes. */
+  int32_t cluster_split; /* 1 = the split_k (2, 4 or 8) k-splits of a tile run as the CTAs of one
+                            thread-block cluster and are summed through distributed shared
+                            memory: no workspace, no global round trip; cta_group must be 1 */
   int32_t stream_k;   /* 1 = stream-K schedule: every CTA takes an equal contiguous share of all
                          (tile, k-block) work; tiles cut between CTAs are reduced through the
                          workspace.  Excludes split_k > 1 and split_tail. */

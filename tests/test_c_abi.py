@@ -98,6 +98,13 @@ def test_config_validation():
         cfg = _lib.Config.from_dict({**dict(tile_n=128, cta_group=1), **bad})
         assert not _lib.config_valid(cfg, "mm", "bfloat16", 1, 512, 512, 512), bad
     assert _lib.config_valid(_lib.Config.from_dict(dict(tile_n=16, swap_ab=1)), "mm", "float16", 1, 8, 512, 512)
+    # cluster split-K: cluster size 2/4/8, tile columns divisible among the CTAs, unpaired tiles only
+    csk = dict(tile_n=64, cta_group=1, split_k=4, cluster_split=1)
+    assert _lib.config_valid(_lib.Config.from_dict(csk), "mm", "bfloat16", 1, 64, 512, 4096)
+    assert _lib.workspace_bytes(_lib.Config.from_dict(csk), "mm", 1, 64, 512, 4096) == 0
+    for bad in (dict(split_k=3), dict(cta_group=2), dict(tile_n=16, swap_ab=1, split_k=8), dict(stream_k=1)):
+        assert not _lib.config_valid(_lib.Config.from_dict({**csk, **bad}), "mm", "bfloat16", 1, 64, 512, 4096), bad
+    assert not _lib.config_valid(_lib.Config.from_dict(csk), "mm", "bfloat16", 1, 64, 512, 128)  # 2 k-blocks, 4 CTAs
 
 
 def test_workspace_sizing():

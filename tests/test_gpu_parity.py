@@ -177,6 +177,32 @@ def test_swapped_variants(tile_n, split_k, device_state):
             assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
 
 
+@pytest.mark.parametrize("split_k", [2, 4, 8])
+def test_cluster_split_k_variants(split_k, device_state):
+    """k-splits as the CTAs of one cluster, reduced through distributed shared memory."""
+    torch.manual_seed(split_k)
+    for tile_n, swap in ((64, 0), (128, 0), (256, 0), (32, 1), (64, 1), (128, 1)):
+        cfg = dict(tile_n=tile_n, cta_group=1, swap_ab=swap, split_k=split_k, cluster_split=1, group_m=1 if swap else 8)
+        for operation, dtype, batch, m, n, k in (("mm", "bfloat16", 1, 333 if not swap else tile_n - 3, 520, 1000),
+                                                 ("addmm", "float16", 1, 256 if not swap else tile_n, 264, 1024),
+                                                 ("bmm", "bfloat16", 2, 200 if not swap else 8, 136, 512)):
+            if not _lib.config_valid(_lib.Config.from_dict(cfg), operation, dtype, batch, m, n, k):
+                continue
+            lead = (batch,) if operation == "bmm" else ()
+            a = torch.randn((*lead, m, k)).to(TD[dtype])
+            bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+            tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+            out, status = run_abi(operation, dtype, tensors, cfg, device_state)
+            assert status == 0
+            assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
+    # deterministic: the partials are added in rank order
+    op, tensors = O.make_inputs("C2b", "bfloat16", scale_down=4)
+    cfg = dict(tile_n=64, cta_group=1, split_k=split_k, cluster_split=1)
+    first, _ = run_abi(op, "bfloat16", tensors, cfg, device_state)
+    again, _ = run_abi(op, "bfloat16", tensors, cfg, device_state)
+    assert torch.equal(first, again)
+
+
 @pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 def test_swiglu_variants(cta_group, dtype, device_state):
