@@ -182,18 +182,27 @@ class GemmLauncher:
         self._ws_ptr = self.workspace.data_ptr() if self.workspace is not None else 0
         self._status_ptr = self.status.data_ptr()
         self._debug = bool(os.environ.get("AYLA_B200_DEBUG"))
+        # Everything that does not change from call to call, converted for the C call once.
+        import ctypes
+
+        self._entry = _lib.load().ayla_b200_gemm
+        self._head = (_lib.OP_CODES[operation], _lib.DTYPE_CODES[dtype])
+        self._tail = (batch, m, n, k, ctypes.byref(self.config), self._ws_ptr or None,
+                      self.workspace.numel() if self.workspace is not None else 0, self._status_ptr)
+        self._has_bias = operation == "addmm"
+        self._device_index = index
 
     def __call__(self, *tensors: torch.Tensor) -> None:
-        if self.operation == "addmm":
+        if self._has_bias:
             bias, a, bt, out = tensors
             bias_ptr = bias.data_ptr()
         else:
             a, bt, out = tensors
-            bias_ptr = 0
-        _lib.gemm(self.operation, self.dtype, bias_ptr, a.data_ptr(), bt.data_ptr(), out.data_ptr(),
-                  self.batch, self.m, self.n, self.k, self.config, self._ws_ptr,
-                  self.workspace.numel() if self.workspace is not None else 0, self._status_ptr,
-                  torch.cuda.current_stream(self.device).cuda_stream)
+            bias_ptr = None
+        code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), out.data_ptr(), *self._tail,
+                           torch.cuda.current_stream(self._device_index).cuda_stream)
+        if code:
+            _lib.check(code)
         if self._debug:
             self.check_status()
 

@@ -215,6 +215,36 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed_graph(fn, launches, rounds=5, collective=True):
+        """Device time per call of a launch-only ``fn`` replayed from a CUDA graph (the host
+        cannot keep up with 20 us kernels from eight processes); max over ranks."""
+        stream = torch.cuda.Stream(device=device)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fn()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(launches):
+                    fn()
+            graph.replay()
+            stream.synchronize()
+            if collective:
+                dist.barrier()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            best = float("inf")
+            for _ in range(rounds):
+                start.record(stream)
+                graph.replay()
+                stop.record(stream)
+                stream.synchronize()
+                best = min(best, start.elapsed_time(stop) / launches)
+        if not collective:
+            return best
+        t = torch.tensor([best], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     def timed_local(fn, reps):
         """Single-GPU reference time on this rank (no collective inside)."""
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -235,7 +265,7 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
         a = torch.randn(count, mm, kk, device=device, dtype=torch.bfloat16)
         bt = torch.randn(count, nn, kk, device=device, dtype=torch.bfloat16)
         out = torch.empty(count, mm, nn, device=device, dtype=torch.bfloat16)
-        ms = timed(lambda: bmm_sharded(a, bt, out, op), steps * 4)
+        ms = timed_graph(lambda: bmm_sharded(a, bt, out, op), 20)
         flops = 2.0 * 64 * mm * nn * kk
         results[name] = {"ms": ms, "tflops": flops / ms / 1e9, "gbs": 2.0 * 64 * (mm * kk + nn * kk + mm * nn) / ms / 1e6,
                          "partition": f"batch 64 -> {count} per rank, no collective"}
@@ -244,7 +274,7 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
             a = torch.randn(64, mm, kk, device=device, dtype=torch.bfloat16)
             bt = torch.randn(64, nn, kk, device=device, dtype=torch.bfloat16)
             out = torch.empty(64, mm, nn, device=device, dtype=torch.bfloat16)
-            one = timed_local(lambda: op(a, bt, out), steps * 4)
+            one = timed_graph(lambda: op(a, bt, out), 20, collective=False)
             results[name]["one_gpu_ms"] = one
             results[name]["speedup_vs_one_gpu"] = one / ms
             del a, bt, out
@@ -267,7 +297,7 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
     if rank == 0:
         mm_op = gemm_op("mm", "bfloat16")
         full_out = torch.empty(big, big, device=device, dtype=torch.bfloat16)
-        one_gpu_ms = timed_local(lambda: mm_op(a, bt_full, full_out), 2)
+        one_gpu_ms = timed_local(lambda: mm_op(a, bt_full, full_out), 3)
         del full_out
     dist.barrier()
     del bt_full
