@@ -67,7 +67,8 @@ typedef struct ayla_b200_config {
   int32_t split_tail; /* wave quantisation: 1 = apply split_k only to the tiles of the last, partial
                          wave; 2 = do those tiles as two half-width units each (split_k must be 1) */
   int32_t l2_prefetch; /* k-blocks (of 64) the TMA producer prefetches into L2 ahead of its
-                          shared-memory loads; 0 = off.  Helps cold, short-K and streaming shapes. */
+                          shared-memory loads; 0 = off.  Measured slower on every shape tried so far;
+                          kept as a tuning knob, never chosen by the default. */
   int32_t cluster_split; /* 1 = the split_k (2, 4 or 8) k-splits of a tile run as the CTAs of one
                             thread-block cluster and are summed through distributed shared
                             memory: no workspace, no global round trip; cta_group must be 1 */
