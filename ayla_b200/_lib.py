@@ -33,6 +33,7 @@ EXPORTS = (
     "ayla_b200_kernel_info",
     "ayla_b200_set_wait_timeout_ms",
     "ayla_b200_debug_set_flags",
+    "ayla_b200_set_launch_overlap",
     "ayla_b200_last_error",
     "ayla_b200_version",
 )
@@ -54,6 +55,7 @@ class Config(ctypes.Structure):
         ("l2_prefetch", ctypes.c_int32),
         ("cluster_split", ctypes.c_int32),
         ("stream_k", ctypes.c_int32),
+        ("tile_rows", ctypes.c_int32),
     ]
 
     FIELDS = tuple(name for name, _ in _fields_)
@@ -61,7 +63,7 @@ class Config(ctypes.Structure):
     @classmethod
     def from_dict(cls, values: dict) -> "Config":
         cfg = cls(tile_n=256, cta_group=1, swap_ab=0, split_k=1, group_m=8, grid_ctas=0,
-                  l2_hint_a=0, l2_hint_b=0, split_tail=0, l2_prefetch=0, cluster_split=0, stream_k=0)
+                  l2_hint_a=0, l2_hint_b=0, split_tail=0, l2_prefetch=0, cluster_split=0, stream_k=0, tile_rows=0)
         for key in cls.FIELDS:
             if key in values and values[key] is not None:
                 setattr(cfg, key, int(values[key]))
@@ -133,6 +135,8 @@ def load() -> ctypes.CDLL:
         lib.ayla_b200_set_wait_timeout_ms.restype = None
         lib.ayla_b200_debug_set_flags.argtypes = [i32]
         lib.ayla_b200_debug_set_flags.restype = None
+        lib.ayla_b200_set_launch_overlap.argtypes = [i32]
+        lib.ayla_b200_set_launch_overlap.restype = None
         lib.ayla_b200_last_error.argtypes = []
         lib.ayla_b200_last_error.restype = ctypes.c_char_p
         lib.ayla_b200_version.argtypes = []
@@ -234,3 +238,8 @@ def swiglu(dtype: str, x_ptr: int, wg_ptr: int, wu_ptr: int, out_ptr: int, m: in
     check(load().ayla_b200_swiglu(
         DTYPE_CODES[dtype], x_ptr, wg_ptr, wu_ptr, out_ptr, m, n, k,
         ctypes.byref(cfg) if cfg is not None else None, status_ptr or None, stream or None))
+
+
+def set_launch_overlap(enabled: bool) -> None:
+    """Allow (default) or forbid a launch to run its set-up under the previous kernel's tail."""
+    load().ayla_b200_set_launch_overlap(1 if enabled else 0)

@@ -23,6 +23,7 @@ from . import _lib
 from .suite import SWEEP_M, SWEEP_NK, _copies, time_interleaved
 
 MAX_WORKSPACE = 512 << 20
+SM_COUNT = 148
 
 BASELINE_SHAPES = [
     ("mm", "bfloat16", 1, 4096, 4096, 4096),
@@ -44,13 +45,18 @@ SWEEP_SHAPES = [("mm", "bfloat16", 1, m, n, k) for n, k in SWEEP_NK for m in SWE
 def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
     k_blocks = -(-k // 64)
     out: list[dict] = []
-    splits = [s for s in (2, 3, 4, 8, 16) if k_blocks >= 4 * s]
+    splits = [s for s in (2, 4, 8, 16) if k_blocks >= 4 * s]
     if m <= 128 and n >= 128:
         widths = sorted({w for w in (16, 32, 64, 128) if w >= min(m, 128)} | {128})
+        # Trimmed tiles: as many rows per tile as spread bt over a whole number of waves.
+        waves = -(-(batch * -(-n // 128)) // SM_COUNT)
+        rows = -(-n * batch // (SM_COUNT * waves))
+        trims = sorted({r for r in (rows, -(-rows // 8) * 8) if 8 <= r < 128}) if batch == 1 else []
         for w in widths[:3]:
             base = dict(tile_n=w, cta_group=1, swap_ab=1, group_m=1)
             out.append(dict(base))
-            out.append(dict(base, stream_k=1))
+            for r in trims:
+                out.append(dict(base, tile_rows=r))
             for s in splits[:3]:
                 out.append(dict(base, split_k=s))
             for s in (2, 4, 8):
@@ -64,17 +70,17 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
                 continue
             base = dict(tile_n=tile_n, cta_group=cta_group, group_m=8)
             out.append(dict(base))
-            out.append(dict(base, stream_k=1))
             if tile_n >= 128:
                 out.append(dict(base, split_tail=2))
             tiles = batch * -(-m // (128 * cta_group)) * -(-n // tile_n)
-            if tiles * cta_group <= 148:
+            if tiles * cta_group <= SM_COUNT:
                 for s in splits[:3]:
                     out.append(dict(base, split_k=s))
-                if cta_group == 1:
-                    for s in (2, 4, 8):
-                        if k_blocks >= 4 * s and tiles * s <= 296:
-                            out.append(dict(base, split_k=s, cluster_split=1))
+                for s in (2, 4, 8):
+                    if s * cta_group <= 4 and k_blocks >= 4 * s and tiles * s * cta_group <= 2 * SM_COUNT:
+                        out.append(dict(base, split_k=s, cluster_split=1))
+                if cta_group == 1 and k_blocks >= 32 and tiles * 8 <= 2 * SM_COUNT:
+                    out.append(dict(base, split_k=8, cluster_split=1))
     return out
 
 

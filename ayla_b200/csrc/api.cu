@@ -71,6 +71,7 @@ std::mutex g_init_mutex;
 PFN_cuTensorMapEncodeTiled g_encode_tiled = nullptr;
 std::atomic<long long> g_timeout_ns{2000000000ll};
 std::atomic<int> g_debug_flags{0};
+std::atomic<int> g_launch_overlap{1};
 
 // ------------------------------------------------------------- tensor maps
 
@@ -154,6 +155,7 @@ struct Plan {
   int cluster_split;    // cluster size of the cluster split-K schedule (0 = not used)
   long long slabs;      // fp32 partial-sum slabs of 128 x tile_n the schedule may write
   int row_tiles;  // 128-row x tile_n tiles (split-K counters, slabs)
+  int tile_rows;  // rows of the row operand per tile (128 unless the swapped form trims it)
 };
 
 int check_shape(int op, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
@@ -198,12 +200,14 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
     return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split must be 0 or 1");
   }
   if (c.cluster_split) {
-    if (swiglu || c.cta_group != 1 || c.stream_k || c.split_tail) {
+    if (swiglu || c.stream_k || c.split_tail) {
       return fail(AYLA_B200_E_UNSUPPORTED,
-                  "cluster_split needs cta_group = 1 and excludes stream_k, split_tail and the SwiGLU kernel");
+                  "cluster_split excludes stream_k, split_tail and the SwiGLU kernel");
     }
-    if (c.split_k != 2 && c.split_k != 4 && c.split_k != 8) {
-      return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split needs split_k in {2, 4, 8} (the cluster size)");
+    // The cluster has split_k * cta_group CTAs, 8 at most.
+    if (c.split_k != 2 && c.split_k != 4 && !(c.split_k == 8 && c.cta_group == 1)) {
+      return fail(AYLA_B200_E_UNSUPPORTED,
+                  "cluster_split needs split_k in {2, 4, 8} and a cluster (split_k * cta_group) of at most 8 CTAs");
     }
     if (c.tile_n % (4 * c.split_k) != 0) {
       return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split needs tile_n to be a multiple of 4 * split_k");
@@ -230,6 +234,9 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
       return fail(AYLA_B200_E_UNSUPPORTED, "the SwiGLU kernel has no split-K or swapped form");
     }
     return AYLA_B200_OK;
+  }
+  if (c.tile_rows != 0 && (!c.swap_ab || c.tile_rows < 8 || c.tile_rows > 128)) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "tile_rows needs swap_ab = 1 and a value between 8 and 128 (0 = 128)");
   }
   if (c.swap_ab) {
     if (c.cta_group != 1) {
@@ -262,7 +269,8 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
   }
   const int out_tile_n = (epilogue == EPI_SWIGLU) ? 128 : tile_n;
   plan->kernel = e;
-  plan->m_tiles = static_cast<int>(ceil_div(rows, 128 * c.cta_group));
+  plan->tile_rows = (c.swap_ab && c.tile_rows > 0) ? c.tile_rows : 128;
+  plan->m_tiles = static_cast<int>(ceil_div(rows, c.swap_ab ? plan->tile_rows : 128 * c.cta_group));
   plan->n_tiles = static_cast<int>(ceil_div(cols, out_tile_n));
   plan->k_blocks = static_cast<int>(ceil_div(k, 64));
   int splits = c.split_k;
@@ -311,15 +319,17 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
   }
   plan->cluster_split = 0;
   if (c.cluster_split) {
-    // One cluster of split_k CTAs per tile, one tile per cluster; every CTA must have a
-    // non-empty share of K.
+    // One cluster of split_k CTAs (CTA pairs) per tile, one tile per cluster; every k-split
+    // must be non-empty.
     const int s_k = c.split_k;
     const int per = static_cast<int>(ceil_div(plan->k_blocks, s_k));
     if (static_cast<int64_t>(s_k - 1) * per >= plan->k_blocks) {
       return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split: %d k-blocks cannot be shared by %d CTAs",
                   plan->k_blocks, s_k);
     }
-    if (tiles * s_k > 0x7FFFFFFF) return fail(AYLA_B200_E_UNSUPPORTED, "too many tiles (%lld)", (long long)tiles);
+    if (tiles * s_k * c.cta_group > 0x7FFFFFFF) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "too many tiles (%lld)", (long long)tiles);
+    }
     plan->cluster_split = s_k;
     plan->splits = s_k;
     plan->kb_per_split = per;
@@ -329,7 +339,7 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
     plan->row_tiles = 0;
     plan->slabs = 0;
     plan->group_m = c.group_m;
-    plan->grid = static_cast<int>(tiles * s_k);
+    plan->grid = static_cast<int>(tiles * s_k * c.cta_group);
     return AYLA_B200_OK;
   }
   // Tiles processed at the same time by the persistent grid.
@@ -491,7 +501,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   LaunchArgs la;
   memset(&la, 0, sizeof(la));
   const int b_box_rows = (e.epilogue == EPI_SWIGLU) ? 128 : e.tile_n / e.cta_group;
-  int rc = encode_map(&la.tm_a, pr.row_operand, pr.k, pr.rows, pr.batch, 64, 128, 1);
+  int rc = encode_map(&la.tm_a, pr.row_operand, pr.k, pr.rows, pr.batch, 64, plan.tile_rows, 1);
   if (rc) return rc;
   rc = encode_map(&la.tm_b, pr.col_operand, pr.k, pr.cols, pr.batch, 64, b_box_rows, 1);
   if (rc) return rc;
@@ -539,6 +549,10 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.timeout_ns = static_cast<unsigned long long>(g_timeout_ns.load());
   p.debug_flags = g_debug_flags.load();
   p.l2_prefetch = c.l2_prefetch;
+  p.tile_rows = plan.tile_rows;
+  // One stage receives this CTA's rows of the row operand and its share of the column
+  // operand; the leader of a pair counts both CTAs' bytes.
+  p.stage_tx = static_cast<uint32_t>((plan.tile_rows + e.tile_n / e.cta_group) * 128 * e.cta_group);
   if (plan.slabs > 0) {
     const size_t need = workspace_bytes_for(plan);
     if (workspace == nullptr || workspace_bytes < need) {
@@ -552,13 +566,14 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
     p.ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + counter_bytes_for(plan));
   }
 #ifdef AYLA_B200_TRACE
-  // Tuning builds: without split-K the workspace receives the per-CTA cycle counters.
-  if (plan.splits <= 1 && workspace != nullptr && workspace_bytes >= (4096 + static_cast<size_t>(plan.grid) * 8) * 8) {
+  // Tuning builds: a schedule that needs no scratch lends the workspace to the per-CTA cycle counters.
+  if (plan.slabs == 0 && workspace != nullptr && workspace_bytes >= (4096 + static_cast<size_t>(plan.grid) * 8) * 8) {
     p.trace = reinterpret_cast<long long*>(workspace);
   }
 #endif
   la.grid = plan.grid;
-  la.cluster_x = plan.cluster_split;
+  la.cluster_x = plan.cluster_split * e.cta_group;
+  la.overlap = g_launch_overlap.load();
   la.stream = stream;
   const cudaError_t err = e.launch(la);
   if (err != cudaSuccess) {
@@ -889,6 +904,8 @@ int ayla_b200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_p
 }
 
 void ayla_b200_debug_set_flags(int flags) { g_debug_flags.store(flags); }
+
+void ayla_b200_set_launch_overlap(int enabled) { g_launch_overlap.store(enabled ? 1 : 0); }
 
 const char* ayla_b200_last_error(void) { return g_last_error.c_str(); }
 

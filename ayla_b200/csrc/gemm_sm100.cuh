@@ -73,6 +73,8 @@ struct KernelParams {
   long long* trace;   // per-CTA cycle counters, written only by AYLA_B200_TRACE builds
   int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
   int l2_prefetch;    // k-blocks the producer prefetches into L2 ahead of its shared-memory loads
+  int tile_rows;      // swapped form: rows of the row operand per tile (8..128); 128 otherwise
+  uint32_t stage_tx;  // bytes one ring stage receives (both CTAs of a pair together)
 };
 
 // Cycle accounting for tuning builds (-DAYLA_B200_TRACE): each role records the
@@ -190,7 +192,8 @@ __device__ __forceinline__ void locate_tile(const KernelParams& p, int tile, int
   const int r = t - g * group_size;
   const int m_t = first_m + r % rows_in_group;
   const int n_t = r / rows_in_group;
-  w.m0 = (m_t * T::CTA_GROUP + cta_rank) * T::BM;
+  // The swapped form may use fewer than 128 rows of its tile (tile_rows).
+  w.m0 = T::TRANS_OUT ? m_t * p.tile_rows : (m_t * T::CTA_GROUP + cta_rank) * T::BM;
   w.n0 = n_t * T::OUT_BN + half * (T::OUT_BN / 2);
   w.tile = tile;
 }
@@ -359,7 +362,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   long long* stamps = (p.trace != nullptr) ? p.trace + 4096 + blockIdx.x * 8 : nullptr;
   if (stamps != nullptr && threadIdx.x == 0) stamps[0] = static_cast<long long>(global_timer_ns());
 #endif
-  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  // A CTA pair is two CTAs whose ranks in the cluster differ in the last bit; with cluster
+  // split-K a cluster holds several pairs, so the leader is the even rank of the pair,
+  // not rank 0 of the cluster.
+  const uint32_t cluster_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const uint32_t cta_rank = cluster_rank & 1u;
+  const uint32_t pair_base = cluster_rank & ~1u;
+  const uint16_t pair_mask = static_cast<uint16_t>(0x3u << pair_base);
   const bool is_leader = cta_rank == 0;
 
   const BoundedWait bw{abort_flag, p.status, p.timeout_ns};
@@ -411,11 +420,20 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (stamps != nullptr && threadIdx.x == 32) stamps[1] = static_cast<long long>(global_timer_ns());
 #endif
 
-  // Cluster split-K (single-CTA tiles only): cluster size, and this CTA's rank in it.
-  const int csk = (CG == 1) ? p.cluster_split : 0;
-  const int csk_rank = csk > 0 ? static_cast<int>(cluster_ctarank()) : 0;
-  const int first_unit = (CG == 2) ? (blockIdx.x >> 1) : (csk > 0 ? blockIdx.x / csk : blockIdx.x);
-  const int unit_stride = (CG == 2) ? (gridDim.x >> 1) : (csk > 0 ? gridDim.x / csk : gridDim.x);
+  // Everything above touched only this launch's own shared memory, TMEM and parameters.
+  // From here on global memory is read and written, so the launch that precedes this one
+  // in the stream must be complete (a no-op unless the launch was allowed to start early);
+  // after that the next launch may begin its own set-up on SMs that fall idle.
+  grid_dependency_wait();
+  grid_launch_dependents();
+
+  // Cluster split-K: the cluster holds `csk` CTAs (CTA pairs when CG == 2), one per k-split
+  // of the cluster's tile.
+  const int csk = (T::EPI != EPI_SWIGLU) ? p.cluster_split : 0;
+  const int csk_rank = csk > 0 ? static_cast<int>(cluster_ctarank()) / CG : 0;
+  const int ctas_per_unit = CG * (csk > 0 ? csk : 1);
+  const int first_unit = blockIdx.x / ctas_per_unit;
+  const int unit_stride = gridDim.x / ctas_per_unit;
 
   // The producer and MMA warps run their loops with all 32 lanes (addresses,
   // coordinates and descriptors are warp-uniform, which lets the compiler keep them
@@ -429,7 +447,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint64_t pol_a = make_policy(p.l2_hint_a);
     const uint64_t pol_b = make_policy(p.l2_hint_b);
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t full_bar0 = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
+    const uint32_t full_bar0 = (CG == 2) ? map_to_cta(bar_full, pair_base) : bar_full;
     uint32_t stage = 0, phase = 0;
     AYLA_TRACE_BEGIN
     UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank, csk_rank);
@@ -457,7 +475,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
         if (issuer) {
           const uint32_t full_bar = full_bar0 + stage * 8;
-          if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, T::STAGE_BYTES * CG);
+          if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, p.stage_tx);
           const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
           const uint32_t sb = sa + T::A_BYTES;
           tma_load_3d<CG>(sa, &tm_a, full_bar, kb * T::BK, w.m0, w.batch, pol_a);
@@ -522,13 +540,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             if constexpr (CG == 1) {
               umma_commit_1cta(bar_empty + stage * 8);
             } else {
-              umma_commit_2cta(bar_empty + stage * 8, 0x3);
+              umma_commit_2cta(bar_empty + stage * 8, pair_mask);
             }
             if (kb == w.kb1 - 1) {
               if constexpr (CG == 1) {
                 umma_commit_1cta(bar_acc_full + acc * 8);
               } else {
-                umma_commit_2cta(bar_acc_full + acc * 8, 0x3);
+                umma_commit_2cta(bar_acc_full + acc * 8, pair_mask);
               }
             }
           }
@@ -571,7 +589,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     constexpr int CHUNK_COLS = T::OUT_BN < 32 ? T::OUT_BN : 32;
     constexpr int EPI_THREADS = T::EPI_WARPS * 32;
     const uint32_t acc_empty_leader =
-        (CG == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
+        (CG == 2) ? map_to_cta(bar_acc_empty, pair_base) : bar_acc_empty;
     AYLA_TRACE_BEGIN
 
     // No early exit in this loop: the warps meet at named barriers, so after an abort
@@ -597,7 +615,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 
-      const bool rows_live = (w.m0 + q * 32) < p.m;
+      // Rows of the tile that exist: the matrix may end inside it, and the swapped form may
+      // give a tile fewer than 128 rows.
+      const int row_end = T::TRANS_OUT ? min(p.m, w.m0 + p.tile_rows) : p.m;
+      const bool rows_live = (w.m0 + q * 32) < row_end;
       const int unit_chunks = w.is_narrow ? CHUNKS32 / 2 : CHUNKS32;
       const int unit_groups = (unit_chunks + 1) / 2;
 
@@ -623,9 +644,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const int row = w.m0 + row_in_tile;
           float bias_v = 0.0f;
           if constexpr (T::EPI == EPI_BIAS) {
-            if (row < p.m) bias_v = load_elem(p.bias, row, is_bf16);
+            if (row < row_end) bias_v = load_elem(p.bias, row, is_bf16);
           }
-          if (row < p.m) {
+          if (row < row_end) {
             uint8_t* base = reinterpret_cast<uint8_t*>(p.out) + 2 * (w.batch * p.out_batch_stride);
 #pragma unroll
             for (int j = 0; j < CHUNK_COLS; ++j) {
@@ -684,48 +705,161 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       };
 
       if (csk > 0) {
-        // ---- cluster split-K: the S CTAs of the cluster hold the S partial sums of this
-        // tile.  Each CTA owns BN / S columns of it: every CTA sends each owner its partial
-        // of the owner's columns through distributed shared memory (into the operand ring,
-        // idle by now), then each owner adds the S partials in rank order and stores.
-        if constexpr (CG == 1 && T::EPI != EPI_SWIGLU) {
+        // ---- cluster split-K: S CTAs of the cluster (those with this CTA's place in its
+        // pair) hold the S partial sums of this 128-row tile.  Each owns BN / S columns of
+        // it: every CTA sends each owner its partial of the owner's columns through
+        // distributed shared memory (into the operand ring, idle by now), then each owner
+        // adds the S partials in split order and stores.
+        if constexpr (T::EPI != EPI_SWIGLU) {
           const int slice_cols = BN / csk;
           const int slice_shift = __ffs(slice_cols) - 1;
           const int slice_c4 = slice_cols >> 2;
           const uint32_t exch = smem_u32(smem);
+          // A CTA keeps its own partial of its own columns in TMEM (no trip through shared
+          // memory) whenever a 32-column TMEM load never straddles two owners.
+          const bool own_in_tmem = slice_cols >= CHUNK_COLS;
           cluster_arrive();  // every CTA's MMAs are done: no ring is being read any more
           cluster_wait();
-          constexpr int STEP = T::TRANS_OUT ? 1 : 2;
-#pragma unroll 1
-          for (int c0 = wsub * STEP; c0 < CHUNKS32; c0 += 2 * STEP) {
-#pragma unroll 1
-            for (int c32 = c0; c32 < c0 + STEP && c32 < CHUNKS32; ++c32) {
-              uint32_t r[32];
-              if constexpr (CHUNK_COLS == 32) {
-                tmem_ld_32x32(t_acc + c32 * 32, r);
-              } else {
-                tmem_ld_32x16(t_acc, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
-              }
-              tmem_ld_wait();
+#ifdef AYLA_B200_TRACE
+          if (stamps != nullptr && warp == 2 && lane == 0) stamps[6] = static_cast<long long>(global_timer_ns());
+#endif
+          auto send_chunk = [&](int c32, const uint32_t (&r)[32]) {
 #pragma unroll
-              for (int j = 0; j < CHUNK_COLS / 4; ++j) {
-                const int col = c32 * 32 + 4 * j;
-                const int owner = col >> slice_shift;
-                const int c4 = (col - (owner << slice_shift)) >> 2;
-                const uint32_t dst =
-                    map_to_cta(exch + ((csk_rank * slice_c4 + c4) * 128 + row_in_tile) * 16, owner);
-                st_cluster_v4(dst, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                              __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            for (int j = 0; j < CHUNK_COLS / 4; ++j) {
+              const int col = c32 * 32 + 4 * j;
+              const int owner = col >> slice_shift;
+              if (own_in_tmem && owner == csk_rank) continue;
+              const int c4 = (col - (owner << slice_shift)) >> 2;
+              const uint32_t dst =
+                  map_to_cta(exch + ((csk_rank * slice_c4 + c4) * 128 + row_in_tile) * 16,
+                             static_cast<uint32_t>(owner * CG) + cta_rank);
+              st_cluster_v4(dst, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            }
+          };
+          {
+            // The chunks that hold other owners' columns, dealt alternately to the two warps
+            // of a lane quarter and sent two at a time (both TMEM loads in flight together).
+            const int own_c0 = own_in_tmem ? (csk_rank << slice_shift) >> 5 : -1;
+            const int own_c1 = own_in_tmem ? own_c0 + (slice_cols >> 5) : -1;
+            int pending = -1, seen = 0;
+            uint32_t ra[32], rb[32];
+#pragma unroll 1
+            for (int c32 = 0; c32 < CHUNKS32; ++c32) {
+              if (c32 >= own_c0 && c32 < own_c1) continue;
+              const bool mine = ((seen++) & 1) == wsub;
+              if (!mine) continue;
+              if constexpr (CHUNK_COLS == 32) {
+                if (pending < 0) {
+                  tmem_ld_32x32(t_acc + c32 * 32, ra);
+                  pending = c32;
+                } else {
+                  tmem_ld_32x32(t_acc + c32 * 32, rb);
+                  tmem_ld_wait();
+                  send_chunk(pending, ra);
+                  send_chunk(c32, rb);
+                  pending = -1;
+                }
+              } else {
+                tmem_ld_32x16(t_acc, *reinterpret_cast<uint32_t(*)[16]>(&ra[0]));
+                tmem_ld_wait();
+                send_chunk(c32, ra);
               }
             }
+            if (pending >= 0) {
+              tmem_ld_wait();
+              send_chunk(pending, ra);
+            }
           }
-          release_accumulator();
           cluster_arrive();  // all partials delivered
           cluster_wait();
+#ifdef AYLA_B200_TRACE
+          if (stamps != nullptr && warp == 2 && lane == 0) stamps[7] = static_cast<long long>(global_timer_ns());
+#endif
+          const float4* mine = reinterpret_cast<const float4*>(smem);
           const int row = w.m0 + row_in_tile;
-          if (row < p.m) {
+          if (own_in_tmem) {
+            // Sum, in split order, the partials of this CTA's columns: its own from TMEM,
+            // the others from the exchange area.  `lc` counts 32-column chunks of the slice.
+            auto reduce_chunk = [&](int lc, const uint32_t (&own)[32], float (&v)[32]) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s = 0; s < csk; ++s) {
+                  float4 x;
+                  if (s == csk_rank) {
+                    x = make_float4(__uint_as_float(own[4 * j]), __uint_as_float(own[4 * j + 1]),
+                                    __uint_as_float(own[4 * j + 2]), __uint_as_float(own[4 * j + 3]));
+                  } else {
+                    x = mine[(s * slice_c4 + lc * 8 + j) * 128 + row_in_tile];
+                  }
+                  sum.x += x.x;
+                  sum.y += x.y;
+                  sum.z += x.z;
+                  sum.w += x.w;
+                }
+                v[4 * j + 0] = sum.x;
+                v[4 * j + 1] = sum.y;
+                v[4 * j + 2] = sum.z;
+                v[4 * j + 3] = sum.w;
+              }
+            };
+            const int first_c32 = (csk_rank << slice_shift) >> 5;  // tile chunk index of the slice
+            const int slice_chunks = slice_cols >> 5;
+            if constexpr (CHUNK_COLS == 32) {
+              if (!T::TRANS_OUT && slice_cols >= 64) {
+                // Whole 64-column groups: through the staging rows and a bulk store, like
+                // the ordinary epilogue.
+#pragma unroll 1
+                for (int g = wsub; 2 * g < slice_chunks; g += 2) {
+                  uint32_t ra[32], rb[32];
+                  tmem_ld_32x32(t_acc + (first_c32 + 2 * g) * 32, ra);
+                  tmem_ld_32x32(t_acc + (first_c32 + 2 * g + 1) * 32, rb);
+                  tmem_ld_wait();
+                  const bool live = rows_live && (w.n0 + ((first_c32 + 2 * g) >> 1) * 64) < p.n;
+                  float v[32];
+                  reduce_chunk(2 * g, ra, v);
+                  if (live) finish_chunk(v, first_c32 + 2 * g);
+                  reduce_chunk(2 * g + 1, rb, v);
+                  if (live) finish_chunk(v, first_c32 + 2 * g + 1);
+                }
+              } else {
+#pragma unroll 1
+                for (int lc = wsub; lc < slice_chunks; lc += 2) {
+                  const int c32 = first_c32 + lc;
+                  uint32_t ra[32];
+                  tmem_ld_32x32(t_acc + c32 * 32, ra);
+                  tmem_ld_wait();
+                  float v[32];
+                  reduce_chunk(lc, ra, v);
+                  const int col0 = w.n0 + c32 * 32;
+                  if (!(rows_live && col0 < p.n)) continue;
+                  if constexpr (T::TRANS_OUT) {
+                    finish_chunk(v, c32);
+                  } else if (row < row_end) {
+                    // A lone 32-column chunk: 64 contiguous bytes of this thread's output row.
+                    if constexpr (T::EPI == EPI_BIAS) {
+#pragma unroll
+                      for (int j = 0; j < 32; ++j) v[j] += smem_bias[bias_buf * BN + c32 * 32 + j];
+                    }
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) +
+                                   2 * (w.batch * p.out_batch_stride + static_cast<long long>(row) * p.out_ld + col0);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      if (col0 + 8 * j < p.n) {
+                        *reinterpret_cast<uint4*>(dst + 16 * j) =
+                            make_uint4(pack2(v[8 * j], v[8 * j + 1], is_bf16), pack2(v[8 * j + 2], v[8 * j + 3], is_bf16),
+                                       pack2(v[8 * j + 4], v[8 * j + 5], is_bf16), pack2(v[8 * j + 6], v[8 * j + 7], is_bf16));
+                      }
+                    }
+                  }
+                }
+              }
+            }
+          } else if (row < row_end) {
+            // Narrow slices (fewer than 32 columns per CTA): every partial, this CTA's own
+            // included, went through the exchange area.
             uint8_t* base = reinterpret_cast<uint8_t*>(p.out) + 2 * (w.batch * p.out_batch_stride);
-            const float4* mine = reinterpret_cast<const float4*>(smem);
             for (int c4 = wsub; c4 < slice_c4; c4 += 2) {
               float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
               for (int s = 0; s < csk; ++s) {
@@ -758,6 +892,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               }
             }
           }
+          release_accumulator();
         }
       } else if (!split_k) {
         if constexpr (!T::TRANS_OUT) {

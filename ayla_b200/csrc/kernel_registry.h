@@ -14,6 +14,7 @@ struct LaunchArgs {
   KernelParams p;
   int grid;
   int cluster_x;  // 0 = the variant's own cluster width (1 or 2)
+  int overlap;    // 1 = the launch may start before the previous launch in the stream ends
   cudaStream_t stream;
 };
 
@@ -44,17 +45,25 @@ cudaError_t launch_variant(const LaunchArgs& a) {
   cfg.blockDim = dim3(T::THREADS, 1, 1);
   cfg.dynamicSmemBytes = T::SMEM_BYTES;
   cfg.stream = a.stream;
-  cudaLaunchAttribute attr[1];
-  cfg.numAttrs = 0;
-  const int cluster_x = (T::CTA_GROUP == 2) ? 2 : a.cluster_x;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  const int cluster_x = a.cluster_x > 0 ? a.cluster_x : T::CTA_GROUP;
   if (cluster_x > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster_x);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
   }
+  if (a.overlap) {
+    // The kernel waits for its predecessor itself (griddepcontrol.wait) before it touches
+    // global memory, so its set-up may run under the predecessor's tail.
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<T>, a.tm_a, a.tm_b, a.tm_b2, a.tm_d, a.p);
 }
 

@@ -20,6 +20,17 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   return r;
 }
 
+// Programmatic dependent launch.  `grid_dependency_wait` returns once every launch this
+// one depends on has completed and its writes are visible (at once when the launch was
+// not allowed to start early); `grid_launch_dependents` lets the next launch in the stream,
+// if it was launched with that permission, start running ahead of this grid's completion.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Address of `local_addr` (a shared::cta address of this CTA) as seen in CTA
 // `rank` of the cluster, in the shared::cluster window.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {

@@ -48,6 +48,7 @@ _DEFAULTS: dict[str, object] = {
     "l2_prefetch": 0,
     "cluster_split": 0,
     "stream_k": 0,
+    "tile_rows": 0,
 }
 
 # A measured schedule is transferred to another shape only when the shapes are

@@ -69,12 +69,17 @@ typedef struct ayla_b200_config {
   int32_t l2_prefetch; /* k-blocks (of 64) the TMA producer prefetches into L2 ahead of its
                           shared-memory loads; 0 = off.  Measured slower on every shape tried so far;
                           kept as a tuning knob, never chosen by the default. */
-  int32_t cluster_split; /* 1 = the split_k (2, 4 or 8) k-splits of a tile run as the CTAs of one
-                            thread-block cluster and are summed through distributed shared
-                            memory: no workspace, no global round trip; cta_group must be 1 */
+  int32_t cluster_split; /* 1 = the split_k (2, 4 or 8) k-splits of a tile run as the CTAs (CTA
+                            pairs when cta_group = 2) of one thread-block cluster and are
+                            summed through distributed shared memory: no workspace, no global
+                            round trip; split_k * cta_group <= 8 */
   int32_t stream_k;   /* 1 = stream-K schedule: every CTA takes an equal contiguous share of all
                          (tile, k-block) work; tiles cut between CTAs are reduced through the
                          workspace.  Excludes split_k > 1 and split_tail. */
+  int32_t tile_rows;  /* swap_ab only: rows of bt per tile, 8..128 (0 = 128).  The MMA still spans
+                         128 rows; fewer rows per tile means more, lighter tiles, so that a
+                         weight whose 128-row tiles would leave SMs idle (112 tiles for
+                         n = 14336 on 148 SMs) is streamed by all of them. */
 } ayla_b200_config;
 
 /*
@@ -202,6 +207,18 @@ AYLA_B200_API void ayla_b200_set_wait_timeout_ms(int64_t ms);
  * 0 restores normal operation.
  */
 AYLA_B200_API void ayla_b200_debug_set_flags(int flags);
+
+/*
+ * Launch overlap (on by default).  Every launch is issued with programmatic stream
+ * serialisation: when the previous operation in the stream is also a kernel, the new grid's
+ * CTAs may become resident and run their set-up (barrier initialisation, TMEM allocation,
+ * descriptor fetch) while that kernel drains; the kernel then executes griddepcontrol.wait,
+ * which returns only when the previous kernel has completed and its writes are visible,
+ * before it touches global memory.  Results are the same as with plain stream order.
+ * 0 switches to plain launches.  No counterpart in the reference (its launcher issues
+ * plain cuLaunchKernel calls, ayla/ptx_runtime.py:237-282).
+ */
+AYLA_B200_API void ayla_b200_set_launch_overlap(int enabled);
 
 AYLA_B200_API const char* ayla_b200_last_error(void);
 AYLA_B200_API const char* ayla_b200_version(void);

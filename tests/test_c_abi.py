@@ -98,13 +98,19 @@ def test_config_validation():
         cfg = _lib.Config.from_dict({**dict(tile_n=128, cta_group=1), **bad})
         assert not _lib.config_valid(cfg, "mm", "bfloat16", 1, 512, 512, 512), bad
     assert _lib.config_valid(_lib.Config.from_dict(dict(tile_n=16, swap_ab=1)), "mm", "float16", 1, 8, 512, 512)
-    # cluster split-K: cluster size 2/4/8, tile columns divisible among the CTAs, unpaired tiles only
+    # cluster split-K: cluster of at most 8 CTAs, tile columns divisible among the k-splits
     csk = dict(tile_n=64, cta_group=1, split_k=4, cluster_split=1)
     assert _lib.config_valid(_lib.Config.from_dict(csk), "mm", "bfloat16", 1, 64, 512, 4096)
     assert _lib.workspace_bytes(_lib.Config.from_dict(csk), "mm", 1, 64, 512, 4096) == 0
-    for bad in (dict(split_k=3), dict(cta_group=2), dict(tile_n=16, swap_ab=1, split_k=8), dict(stream_k=1)):
+    assert _lib.config_valid(_lib.Config.from_dict({**csk, "cta_group": 2}), "mm", "bfloat16", 1, 64, 512, 4096)
+    for bad in (dict(split_k=3), dict(cta_group=2, split_k=8), dict(tile_n=16, swap_ab=1, split_k=8), dict(stream_k=1)):
         assert not _lib.config_valid(_lib.Config.from_dict({**csk, **bad}), "mm", "bfloat16", 1, 64, 512, 4096), bad
     assert not _lib.config_valid(_lib.Config.from_dict(csk), "mm", "bfloat16", 1, 64, 512, 128)  # 2 k-blocks, 4 CTAs
+    # trimmed tiles exist only in the swapped form
+    trimmed = dict(tile_n=16, swap_ab=1, tile_rows=97)
+    assert _lib.config_valid(_lib.Config.from_dict(trimmed), "mm", "bfloat16", 1, 8, 14336, 4096)
+    for bad in (dict(tile_rows=4), dict(tile_rows=129), dict(swap_ab=0, tile_n=64)):
+        assert not _lib.config_valid(_lib.Config.from_dict({**trimmed, **bad}), "mm", "bfloat16", 1, 8, 14336, 4096), bad
 
 
 def test_workspace_sizing():

@@ -177,6 +177,25 @@ def test_swapped_variants(tile_n, split_k, device_state):
             assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
 
 
+@pytest.mark.parametrize("tile_rows", [8, 56, 97, 104, 120])
+def test_swapped_tiles_with_fewer_rows(tile_rows, device_state):
+    """tile_rows < 128: more, lighter tiles of bt; rows past the trimmed tile are never stored."""
+    torch.manual_seed(tile_rows)
+    for tile_n, split in ((16, dict()), (32, dict(split_k=2)), (64, dict(split_k=2, cluster_split=1)), (128, dict())):
+        cfg = dict(tile_n=tile_n, cta_group=1, swap_ab=1, group_m=1, tile_rows=tile_rows, **split)
+        for operation, dtype, batch, m, n, k in (("mm", "bfloat16", 1, min(tile_n, 24), 1000, 512),
+                                                 ("addmm", "float16", 1, tile_n, 776, 320),
+                                                 ("bmm", "bfloat16", 2, max(1, tile_n - 5), 264, 256)):
+            assert _lib.config_valid(_lib.Config.from_dict(cfg), operation, dtype, batch, m, n, k), cfg
+            lead = (batch,) if operation == "bmm" else ()
+            a = torch.randn((*lead, m, k)).to(TD[dtype])
+            bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+            tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+            out, status = run_abi(operation, dtype, tensors, cfg, device_state)
+            assert status == 0
+            assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
+
+
 @pytest.mark.parametrize("split_k", [2, 4, 8])
 def test_cluster_split_k_variants(split_k, device_state):
     """k-splits as the CTAs of one cluster, reduced through distributed shared memory."""
@@ -201,6 +220,78 @@ def test_cluster_split_k_variants(split_k, device_state):
     first, _ = run_abi(op, "bfloat16", tensors, cfg, device_state)
     again, _ = run_abi(op, "bfloat16", tensors, cfg, device_state)
     assert torch.equal(first, again)
+
+
+@pytest.mark.parametrize("split_k", [2, 4])
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_paired_cluster_split_k_variants(split_k, tile_n, device_state):
+    """k-splits of a 256-row tile as the CTA pairs of one cluster (4 or 8 CTAs)."""
+    torch.manual_seed(split_k * 1000 + tile_n)
+    cfg = dict(tile_n=tile_n, cta_group=2, split_k=split_k, cluster_split=1, group_m=2)
+    for operation, dtype, batch, m, n, k in (("mm", "bfloat16", 1, 333, 520, 1000), ("mm", "float16", 1, 256, 256, 512),
+                                             ("addmm", "float16", 1, 512, 264, 1024), ("addmm", "bfloat16", 1, 130, 72, 2048),
+                                             ("bmm", "bfloat16", 2, 200, 136, 512), ("mm", "bfloat16", 1, 1024, 1024, 4096)):
+        assert _lib.config_valid(_lib.Config.from_dict(cfg), operation, dtype, batch, m, n, k)
+        assert _lib.workspace_bytes(_lib.Config.from_dict(cfg), operation, batch, m, n, k) == 0
+        lead = (batch,) if operation == "bmm" else ()
+        a = torch.randn((*lead, m, k)).to(TD[dtype])
+        bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+        tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+        out, status = run_abi(operation, dtype, tensors, cfg, device_state)
+        assert status == 0
+        assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
+        again, _ = run_abi(operation, dtype, tensors, cfg, device_state)
+        assert torch.equal(out, again)
+
+
+def test_launch_overlap_keeps_stream_order(device_state):
+    """A chain of launches, each reading what the one before wrote, gives the same bits whether
+    or not a launch may start its set-up under its predecessor's tail."""
+    torch.manual_seed(5)
+    n = 1024
+    x0 = torch.randn(256, n).to(torch.bfloat16).to(DEV)
+    weights = [(torch.randn(n, n) * n ** -0.5).to(torch.bfloat16).to(DEV) for _ in range(3)]
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device=DEV)
+    schedules = [dict(tile_n=128, cta_group=2), dict(tile_n=64, cta_group=1, split_k=4),
+                 dict(tile_n=64, cta_group=1, split_k=4, cluster_split=1), dict(tile_n=128, cta_group=1, split_tail=2)]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def chain():
+        bufs = [x0, torch.zeros_like(x0), torch.zeros_like(x0)]
+        cur = 0
+        for step in range(24):
+            src, dst = bufs[cur], bufs[1 + (step % 2)]
+            cfg = _lib.Config.from_dict(schedules[step % len(schedules)])
+            _lib.gemm("mm", "bfloat16", 0, src.data_ptr(), weights[step % 3].data_ptr(), dst.data_ptr(),
+                      1, 256, n, n, cfg, ws.data_ptr(), ws.numel(), 0, stream)
+            cur = 1 + (step % 2)
+        torch.cuda.synchronize()
+        return bufs[cur].clone()
+
+    try:
+        _lib.set_launch_overlap(False)
+        plain = chain()
+        _lib.set_launch_overlap(True)
+        overlapped = chain()
+        out_buf = torch.zeros_like(x0)
+        mid = torch.zeros_like(x0)
+        cfg = _lib.Config.from_dict(schedules[0])
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            cap = torch.cuda.current_stream().cuda_stream
+            _lib.gemm("mm", "bfloat16", 0, x0.data_ptr(), weights[0].data_ptr(), mid.data_ptr(), 1, 256, n, n,
+                      cfg, 0, 0, 0, cap)
+            _lib.gemm("mm", "bfloat16", 0, mid.data_ptr(), weights[1].data_ptr(), out_buf.data_ptr(), 1, 256, n, n,
+                      cfg, 0, 0, 0, cap)
+        graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_launch_overlap(True)
+    assert torch.equal(plain, overlapped)
+    assert torch.isfinite(plain.float()).all()
+    expect_mid = O.gemm_ref32("mm", x0.cpu(), weights[0].cpu()).to(torch.bfloat16)
+    expect = O.gemm_ref32("mm", expect_mid, weights[1].cpu())
+    assert_parity(out_buf.cpu(), expect, "two dependent launches in a graph")
 
 
 @pytest.mark.parametrize("cta_group", [1, 2])
