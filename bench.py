@@ -350,6 +350,12 @@ def main() -> None:
 
     value = world * FLOPS / ms / 1e9
     achieved = FLOPS / ms / 1e9
+    # Denominator: the timed region is a long back-to-back loop, so when the clock record shows
+    # it ran under the power cap the sustained cuBLAS figure is the matching peak; a short run
+    # that was never capped is compared with the burst figure.
+    capped = "sw_power_cap" in (clocks or {}).get("reasons", []) and peaks["bf16_sustained"] > 0
+    peak = peaks["bf16_sustained"] if capped else peaks["bf16"]
+    peak_kind = "sustained (timed loop ran under sw_power_cap)" if capped else "burst"
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -363,10 +369,10 @@ def main() -> None:
                 "h2d_bytes_per_step": int(2 * (M * K + N * K)), "d2h_bytes_per_step": int(2 * M * N),
                 "api": "gemm_op('mm','bfloat16')(a, bt, out) with pinned host operands copied in and out every step"},
         "gpu_launches": args.steps,
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["bf16"], "traffic": NCU_TRAFFIC_BYTES,
-                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "algorithmic_bytes": ALGO_BYTES,
-                     "frac_of_nominal_2250": achieved / 2250.0},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                     "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind}", "algorithmic_bytes": ALGO_BYTES,
+                     "frac_of_burst_peak": achieved / peaks["bf16"], "frac_of_nominal_2250": achieved / 2250.0},
         "parity": {"fro_rel": parity.fro_rel, "max_over_rms": parity.max_over_rms,
                    "over_bound": parity.over_bound, "over_bound_one_ulp": parity.over_bound_one_ulp},
     }
