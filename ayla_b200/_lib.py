@@ -22,6 +22,7 @@ E_INVALID, E_UNSUPPORTED, E_WORKSPACE, E_CUDA, E_NOT_INIT = 1, 2, 3, 4, 5
 EXPORTS = (
     "ayla_b200_init",
     "ayla_b200_gemm",
+    "ayla_b200_gemm_act",
     "ayla_b200_gemm_static_scratch",
     "ayla_b200_swiglu",
     "ayla_b200_default_config",
@@ -112,6 +113,8 @@ def load() -> ctypes.CDLL:
         lib.ayla_b200_init.restype = i32
         lib.ayla_b200_gemm.argtypes = [i32, i32, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, sz, vp, vp]
         lib.ayla_b200_gemm.restype = i32
+        lib.ayla_b200_gemm_act.argtypes = [i32, i32, i32, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, sz, vp, vp]
+        lib.ayla_b200_gemm_act.restype = i32
         lib.ayla_b200_gemm_static_scratch.argtypes = [i32, i32, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, vp]
         lib.ayla_b200_gemm_static_scratch.restype = i32
         lib.ayla_b200_swiglu.argtypes = [i32, vp, vp, vp, vp, i64, i64, i64, cfgp, vp, vp]
@@ -211,6 +214,19 @@ def gemm(op: str, dtype: str, bias_ptr: int, a_ptr: int, bt_ptr: int, out_ptr: i
     check(load().ayla_b200_gemm(
         OP_CODES[op], DTYPE_CODES[dtype], bias_ptr or None, a_ptr, bt_ptr, out_ptr, batch, m, n, k,
         ctypes.byref(cfg) if cfg is not None else None, workspace_ptr or None, workspace_size,
+        status_ptr or None, stream or None))
+
+
+ACT_CODES = {"none": 0, "relu": 1, "sigmoid": 2, "silu": 3, "gelu": 4, "gelu_tanh": 5}
+
+
+def gemm_act(op: str, dtype: str, activation: str, bias_ptr: int, a_ptr: int, bt_ptr: int, out_ptr: int,
+             batch: int, m: int, n: int, k: int, cfg: Config | None, workspace_ptr: int, workspace_size: int,
+             status_ptr: int, stream: int) -> None:
+    """``gemm`` with ``activation`` applied to the fp32 result before it is rounded."""
+    check(load().ayla_b200_gemm_act(
+        OP_CODES[op], DTYPE_CODES[dtype], ACT_CODES[activation], bias_ptr or None, a_ptr, bt_ptr, out_ptr,
+        batch, m, n, k, ctypes.byref(cfg) if cfg is not None else None, workspace_ptr or None, workspace_size,
         status_ptr or None, stream or None))
 
 

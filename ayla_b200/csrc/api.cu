@@ -496,7 +496,7 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
 int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, int is_bf16,
                 const void* bias, const void* b2_operand, void* out, int64_t out_rows,
                 int64_t out_cols, void* workspace, size_t workspace_bytes, uint32_t* status,
-                cudaStream_t stream) {
+                cudaStream_t stream, int activation = 0) {
   const KernelEntry& e = *plan.kernel;
   LaunchArgs la;
   memset(&la, 0, sizeof(la));
@@ -550,6 +550,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.debug_flags = g_debug_flags.load();
   p.l2_prefetch = c.l2_prefetch;
   p.tile_rows = plan.tile_rows;
+  p.act = activation;
   // One stage receives this CTA's rows of the row operand and its share of the column
   // operand; the leader of a pair counts both CTAs' bytes.
   p.stage_tx = static_cast<uint32_t>((plan.tile_rows + e.tile_n / e.cta_group) * 128 * e.cta_group);
@@ -720,8 +721,19 @@ size_t ayla_b200_workspace_counter_bytes(const ayla_b200_config* cfg, int op, in
 int ayla_b200_gemm(int op, int dtype, const void* bias, const void* a, const void* bt, void* out,
                    int64_t batch, int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg,
                    void* workspace, size_t workspace_bytes, uint32_t* status, void* stream) {
+  return ayla_b200_gemm_act(op, dtype, AYLA_B200_ACT_NONE, bias, a, bt, out, batch, m, n, k, cfg, workspace,
+                            workspace_bytes, status, stream);
+}
+
+int ayla_b200_gemm_act(int op, int dtype, int activation, const void* bias, const void* a, const void* bt,
+                       void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
+                       const ayla_b200_config* cfg, void* workspace, size_t workspace_bytes,
+                       uint32_t* status, void* stream) {
   int rc = check_shape(op, dtype, batch, m, n, k);
   if (rc) return rc;
+  if (activation < AYLA_B200_ACT_NONE || activation > AYLA_B200_ACT_GELU_TANH) {
+    return fail(AYLA_B200_E_INVALID, "unknown activation %d", activation);
+  }
   if (a == nullptr || bt == nullptr || out == nullptr) {
     return fail(AYLA_B200_E_INVALID, "a, bt and out must be non-null");
   }
@@ -764,7 +776,7 @@ int ayla_b200_gemm(int op, int dtype, const void* bias, const void* a, const voi
   rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan);
   if (rc) return rc;
   return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, workspace,
-                     workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream));
+                     workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream), activation);
 }
 
 int ayla_b200_gemm_static_scratch(int op, int dtype, const void* bias, const void* a, const void* bt,

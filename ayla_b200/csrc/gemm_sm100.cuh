@@ -73,6 +73,7 @@ struct KernelParams {
   long long* trace;   // per-CTA cycle counters, written only by AYLA_B200_TRACE builds
   int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
   int l2_prefetch;    // k-blocks the producer prefetches into L2 ahead of its shared-memory loads
+  int act;            // activation applied to the fp32 result (after the bias) before rounding: ACT_*
   int tile_rows;      // swapped form: rows of the row operand per tile (8..128); 128 otherwise
   uint32_t stage_tx;  // bytes one ring stage receives (both CTAs of a pair together)
 };
@@ -322,6 +323,30 @@ __device__ __forceinline__ void store_elem(void* base, long long i, float v, int
 __device__ __forceinline__ float silu_mul(float g, float u) {
   const float e = exp2f(-g * 1.4426950408889634f);
   return __fdividef(g, 1.0f + e) * u;
+}
+
+// Activations of the fused epilogue, evaluated on the fp32 accumulator before the single
+// rounding to the output type, as the reference's fused sigmoid is
+// (ayla/passes/lower_to_ptx_template.py:84-113).
+enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_SIGMOID = 2, ACT_SILU = 3, ACT_GELU = 4, ACT_GELU_TANH = 5 };
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case ACT_RELU:
+      return fmaxf(x, 0.0f);
+    case ACT_SIGMOID:
+      return __fdividef(1.0f, 1.0f + exp2f(-x * 1.4426950408889634f));
+    case ACT_SILU:
+      return __fdividef(x, 1.0f + exp2f(-x * 1.4426950408889634f));
+    case ACT_GELU:
+      return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+    case ACT_GELU_TANH: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanhf(u));
+    }
+    default:
+      return x;
+  }
 }
 
 __device__ __forceinline__ uint64_t make_policy(uint32_t hint) {
@@ -582,6 +607,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int epi_tid = (warp - 2) * 32 + lane;      // 0..255
     const int row_in_tile = q * 32 + lane;
     const int is_bf16 = p.is_bf16;
+    const int act = p.act;
     uint8_t* my_store = smem_store + (warp - 2) * T::STORE_BUF_BYTES;
     uint32_t acc = 0, acc_phase = 0;
     uint32_t bias_buf = 0;
@@ -651,7 +677,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < CHUNK_COLS; ++j) {
               const int col = w.n0 + c32 * 32 + j;
-              if (col < p.n) store_elem(base, col * p.out_ld + row, v[j] + bias_v, is_bf16);
+              if (col < p.n) store_elem(base, col * p.out_ld + row, apply_act(v[j] + bias_v, act), is_bf16);
             }
           }
         } else {
@@ -665,6 +691,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               v[4 * j + 2] += b.z;
               v[4 * j + 3] += b.w;
             }
+          }
+          if (act != ACT_NONE) {
+#pragma unroll
+            for (int j = 0; j < CHUNK_COLS; ++j) v[j] = apply_act(v[j], act);
           }
           // Two 32-column chunks fill one 64-column (128-byte) store row.
           const int half = c32 & 1;
@@ -842,6 +872,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
                       for (int j = 0; j < 32; ++j) v[j] += smem_bias[bias_buf * BN + c32 * 32 + j];
                     }
+                    if (act != ACT_NONE) {
+#pragma unroll
+                      for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
+                    }
                     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) +
                                    2 * (w.batch * p.out_batch_stride + static_cast<long long>(row) * p.out_ld + col0);
 #pragma unroll
@@ -877,13 +911,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   if constexpr (T::EPI == EPI_BIAS) bias_v = load_elem(p.bias, row, is_bf16);
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
-                    if (col + j < p.n) store_elem(base, (col + j) * p.out_ld + row, v4[j] + bias_v, is_bf16);
+                    if (col + j < p.n) store_elem(base, (col + j) * p.out_ld + row, apply_act(v4[j] + bias_v, act), is_bf16);
                   }
                 } else {
                   if constexpr (T::EPI == EPI_BIAS) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) v4[j] += load_elem(p.bias, col + j, is_bf16);
                   }
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) v4[j] = apply_act(v4[j], act);
                   uint2 pk;
                   pk.x = pack2(v4[0], v4[1], is_bf16);
                   pk.y = pack2(v4[2], v4[3], is_bf16);

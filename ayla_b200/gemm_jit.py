@@ -33,6 +33,7 @@ from .torch_custom_call import DEFAULT_NAMESPACE, OperandKind, TensorSpec
 _SHORT_DTYPES = {"float16": "f16", "bfloat16": "bf16"}
 _TORCH_DTYPES = {"float16": torch.float16, "bfloat16": torch.bfloat16}
 _OPERATIONS = ("mm", "addmm", "bmm")
+ACTIVATIONS = ("none", "relu", "sigmoid", "silu", "gelu", "gelu_tanh")
 
 # Table entries omit default fields.
 _DEFAULTS: dict[str, object] = {
@@ -167,9 +168,9 @@ class GemmLauncher:
     """
 
     def __init__(self, operation: str, dtype: str, batch: int, m: int, n: int, k: int,
-                 seed: GemmScheduleSeed, device: torch.device):
+                 seed: GemmScheduleSeed, device: torch.device, activation: str = "none"):
         assert seed.builder_config is not None
-        self.operation, self.dtype = operation, dtype
+        self.operation, self.dtype, self.activation = operation, dtype, activation
         self.batch, self.m, self.n, self.k = batch, m, n, k
         self.seed = seed
         self.device = device
@@ -186,8 +187,8 @@ class GemmLauncher:
         # Everything that does not change from call to call, converted for the C call once.
         import ctypes
 
-        self._entry = _lib.load().ayla_b200_gemm
-        self._head = (_lib.OP_CODES[operation], _lib.DTYPE_CODES[dtype])
+        self._entry = _lib.load().ayla_b200_gemm_act
+        self._head = (_lib.OP_CODES[operation], _lib.DTYPE_CODES[dtype], _lib.ACT_CODES[activation])
         self._tail = (batch, m, n, k, ctypes.byref(self.config), self._ws_ptr or None,
                       self.workspace.numel() if self.workspace is not None else 0, self._status_ptr)
         self._has_bias = operation == "addmm"
@@ -219,24 +220,32 @@ class GemmLauncher:
             )
 
 
-def _template(operation: str, dtype: str) -> OpTemplate:
+def _op_name(operation: str, dtype: str, activation: str = "none") -> str:
+    middle = "" if activation == "none" else f"_{activation}"
+    return f"jit_{operation}{middle}_{_SHORT_DTYPES[dtype]}"
+
+
+def _template(operation: str, dtype: str, activation: str = "none") -> OpTemplate:
     torch_dtype = _TORCH_DTYPES[dtype]
     rank = 3 if operation == "bmm" else 2
     tensor = TensorSpec(torch_dtype, (None,) * rank)
     signature = (tensor, tensor, tensor)
     if operation == "addmm":
         signature = (TensorSpec(torch_dtype, (None,)), *signature)
-    return OpTemplate(f"jit_{operation}_{_SHORT_DTYPES[dtype]}", signature)
+    return OpTemplate(_op_name(operation, dtype, activation), signature)
 
 
-def gemm_jit_compiler(operation: str, dtype: str) -> ShapeSpecializingJITCompiler:
+def gemm_jit_compiler(operation: str, dtype: str, activation: str = "none") -> ShapeSpecializingJITCompiler:
     """Per-shape dispatcher for one op: validates operands, picks the schedule once
-    per ``(device, shapes)`` and launches (ayla/gemm_jit.py:339-393)."""
+    per ``(device, shapes)`` and launches (ayla/gemm_jit.py:339-393).  ``activation``
+    (one of ``ACTIVATIONS``) is fused into the epilogue."""
     if operation not in _OPERATIONS:
         raise ValueError(f"unsupported GEMM operation {operation}")
     if dtype not in _SHORT_DTYPES:
         raise ValueError(f"unsupported GEMM dtype {dtype}")
-    template = _template(operation, dtype)
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"unsupported GEMM activation {activation}")
+    template = _template(operation, dtype, activation)
 
     def compile_specialization(bound: OpTemplate, device: torch.device) -> GemmLauncher:
         *bias, a, bt, out = (spec.sizes for spec in bound.signature)
@@ -255,7 +264,7 @@ def gemm_jit_compiler(operation: str, dtype: str) -> ShapeSpecializingJITCompile
         schedule = select_gemm_schedule(operation, dtype, m, n, k, *batch)
         if schedule is None:
             raise ValueError(f"{bound.name}: no schedule for {operation} {lead}x{m}x{n}x{k}")
-        return GemmLauncher(operation, dtype, batch[0] if batch else 1, m, n, k, schedule, device)
+        return GemmLauncher(operation, dtype, batch[0] if batch else 1, m, n, k, schedule, device, activation)
 
     return ShapeSpecializingJITCompiler(template, compile_specialization)
 
@@ -287,3 +296,27 @@ def gemm_op_compiler(operation: str, dtype: str,
     size and the launchers' status words)."""
     gemm_op(operation, dtype, namespace)
     return _COMPILERS[(operation, dtype, namespace)]
+
+
+def gemm_act_op(operation: str, activation: str, dtype: str,
+                namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
+    """Torch op ``(bias?, a, bt, out) -> ()`` writing ``out = activation([bias +] a @ bt^T)``,
+    named ``jit_{operation}_{activation}_{f16|bf16}``; the activation is evaluated on the fp32
+    accumulator before the single rounding.  The reference has one such kernel, a fixed
+    4096-cube matmul + sigmoid (ayla/gemm_collection/auto_matmul_4096_wgmma256_wg_sigmoid.py:22-142);
+    this is the same fusion for every shape, operation and activation in ``ACTIVATIONS``.
+    ``activation="none"`` returns ``gemm_op(operation, dtype)``."""
+    if activation == "none":
+        return gemm_op(operation, dtype, namespace)
+    return _gemm_act_op(operation, activation, dtype, namespace)
+
+
+@cache
+def _gemm_act_op(operation: str, activation: str, dtype: str, namespace: str) -> torch._ops.OpOverload:
+    from .torch_custom_call import make_torch_custom_call
+
+    compiler = gemm_jit_compiler(operation, dtype, activation)
+    _COMPILERS[(f"{operation}_{activation}", dtype, namespace)] = compiler
+    inputs = 3 if operation == "addmm" else 2
+    return make_torch_custom_call(compiler, [OperandKind.R] * inputs + [OperandKind.RW],
+                                  namespace=namespace)

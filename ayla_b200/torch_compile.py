@@ -1,4 +1,5 @@
-"""Route ``aten.mm/addmm/bmm`` in ``torch.compile`` graphs to the sm_100a GEMM ops.
+"""Route ``aten.mm/addmm/bmm`` in ``torch.compile`` graphs to the sm_100a GEMM ops, with a
+following relu / sigmoid / silu / gelu or a SwiGLU gate fused into the GEMM's epilogue.
 
 Same contract as the reference's Inductor integration (ayla/torch_compile.py:652-775):
 ``install()`` claims contiguous NT-layout fp16/bf16 GEMMs on CUDA -- ``lhs`` contiguous,
@@ -23,7 +24,8 @@ import torch
 from torch._inductor import config as inductor_config
 from torch._inductor.custom_graph_pass import CustomGraphPass, get_hash_for_files
 
-from .gemm_jit import _SHORT_DTYPES, _TORCH_DTYPES, gemm_jit_compiler, gemm_op, select_gemm_schedule
+from .gemm_jit import (_SHORT_DTYPES, _TORCH_DTYPES, _op_name, gemm_jit_compiler, gemm_op,
+                       select_gemm_schedule)
 from .torch_custom_call import DEFAULT_NAMESPACE, OperandKind, make_torch_custom_call
 
 aten = torch.ops.aten
@@ -31,11 +33,12 @@ _DTYPE_NAMES = {torch.float16: "float16", torch.bfloat16: "bfloat16"}
 
 
 @cache
-def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
-    """Functional form ``(bias?, a, bt) -> out`` of ``gemm_op`` (the result is allocated by
-    the op), the form a functional FX graph can hold.  Counterpart of the reference's
-    allocating ops (ayla/gemm_collection/dynamic_m.py:90-121)."""
-    compiler = gemm_jit_compiler(operation, dtype)
+def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE,
+               activation: str = "none") -> torch._ops.OpOverload:
+    """Functional form ``(bias?, a, bt) -> out`` of ``gemm_op`` / ``gemm_act_op`` (the result is
+    allocated by the op), the form a functional FX graph can hold.  Counterpart of the
+    reference's allocating ops (ayla/gemm_collection/dynamic_m.py:90-121)."""
+    compiler = gemm_jit_compiler(operation, dtype, activation)
 
     def infer(*inputs: torch.Tensor):
         a, bt = inputs[-2], inputs[-1]
@@ -46,7 +49,7 @@ def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE) -
         compiler,
         [OperandKind.R] * inputs + [OperandKind.RESULT],
         namespace=namespace,
-        name=f"jit_{operation}_{_SHORT_DTYPES[dtype]}_fn",
+        name=f"{_op_name(operation, dtype, activation)}_fn",
         infer_result_shapes=infer,
     )
 
@@ -218,6 +221,179 @@ def route_swiglu(graph: torch.fx.Graph) -> int:
     return rewritten
 
 
+def _is_call(node, target) -> bool:
+    return isinstance(node, torch.fx.Node) and node.op == "call_function" and node.target is target
+
+
+def _close(value, want: float) -> bool:
+    return isinstance(value, (int, float)) and abs(float(value) - want) < 1e-6
+
+
+def _gelu_source(node):
+    """If ``node`` computes the erf form of gelu(x) as Inductor's decompositions leave it for
+    16-bit inputs, ``cvt16(mul(mul(x32, 0.5), add(erf(mul(x32, 1/sqrt 2)), 1)))``, return
+    (x, chain); else None."""
+    chain = [node]
+    inner = _strip_convert(node)
+    if inner is not node:
+        chain.append(inner)
+    if not _is_call(inner, aten.mul.Tensor):
+        return None
+    for half, one_plus in (inner.args, inner.args[::-1]):
+        if not (_is_call(half, aten.mul.Tensor) and _is_call(one_plus, aten.add.Tensor)):
+            continue
+        if not (_close(half.args[1], 0.5) and _close(one_plus.args[1], 1.0)):
+            continue
+        erf = one_plus.args[0]
+        if not (_is_call(erf, aten.erf.default) and _is_call(erf.args[0], aten.mul.Tensor)):
+            continue
+        scaled = erf.args[0]
+        if not _close(scaled.args[1], 0.7071067811865476):
+            continue
+        x32 = half.args[0]
+        if scaled.args[0] is not x32:
+            continue
+        src = _strip_convert(x32, torch.float32)
+        chain += [half, one_plus, erf, scaled] + ([x32] if x32 is not src else [])
+        return src, chain
+    return None
+
+
+def _activation_source(node):
+    """If ``node`` is an activation this library fuses, return (name, input node, nodes of the
+    chain); else None."""
+    if not isinstance(node, torch.fx.Node) or node.op != "call_function":
+        return None
+    if node.target is aten.relu.default:
+        return "relu", node.args[0], [node]
+    if node.target is aten.gelu.default:
+        approximate = node.kwargs.get("approximate", "none")
+        return ("gelu_tanh" if approximate == "tanh" else "gelu"), node.args[0], [node]
+    inner = _strip_convert(node)
+    if _is_call(inner, aten.sigmoid.default):
+        src = _strip_convert(inner.args[0], torch.float32)
+        chain = [node] + ([inner] if inner is not node else []) + ([inner.args[0]] if inner.args[0] is not src else [])
+        return "sigmoid", src, chain
+    found = _silu_source(node)
+    if found is not None:
+        return "silu", found[0], found[1]
+    found = _gelu_source(node)
+    if found is not None:
+        return "gelu", found[0], found[1]
+    return None
+
+
+def _gemm_operands(node):
+    """(operation, lhs, rhs, bias) of an aten GEMM node this pass may claim, else None."""
+    if _is_call(node, aten.mm.default) and len(node.args) == 2:
+        return "mm", node.args[0], node.args[1], None
+    if _is_call(node, aten.bmm.default) and len(node.args) == 2:
+        return "bmm", node.args[0], node.args[1], None
+    if _is_call(node, aten.addmm.default) and len(node.args) == 3:
+        if node.kwargs.get("beta", 1) != 1 or node.kwargs.get("alpha", 1) != 1:
+            return None
+        return "addmm", node.args[1], node.args[2], node.args[0]
+    return None
+
+
+def route_activations(graph: torch.fx.Graph) -> int:
+    """Rewrite ``act(gemm)`` -- relu, sigmoid, silu or gelu applied to a claimed mm/addmm/bmm
+    that nothing else reads -- into one call of the op with the activation fused into its
+    epilogue.  The reference fuses a lone sigmoid onto its fixed 4096-cube matmul under the
+    same single-reader condition (ayla/torch_compile.py:532-547)."""
+    rewritten = 0
+    for node in list(graph.nodes):
+        found = _activation_source(node)
+        if found is None:
+            continue
+        activation, src, chain = found
+        operands = _gemm_operands(src)
+        if operands is None:
+            continue
+        nv, sv = _val(node), _val(src)
+        if nv is None or sv is None or nv.dtype != sv.dtype:
+            continue  # an fp32 step inside a chain: the match is made at the chain's last node
+        operation, lhs, rhs, bias = operands
+        claim = _claim(operation, lhs, rhs, bias)
+        if claim is None:
+            continue
+        members = set(chain)
+        if not (_only_used_by(src, members) and all(_only_used_by(n, members) for n in chain if n is not node)):
+            continue  # the plain product (or a step of the chain) is needed elsewhere
+        dtype = claim[0]
+        with graph.inserting_before(node):
+            perm = [0, 2, 1] if operation == "bmm" else [1, 0]
+            bt = graph.call_function(aten.permute.default, (rhs, perm))
+            bt.meta["val"] = _val(rhs).permute(perm)
+            args = (lhs, bt) if bias is None else (bias, lhs, bt)
+            new = graph.call_function(gemm_fn_op(operation, dtype, DEFAULT_NAMESPACE, activation), args)
+            new.meta.update({k: v for k, v in node.meta.items() if k != "original_aten"})
+        node.replace_all_uses_with(new)
+        graph.erase_node(node)
+        rewritten += 1
+    if rewritten:
+        graph.eliminate_dead_code()
+    return rewritten
+
+
+def route_swiglu_concat(graph: torch.fx.Graph) -> int:
+    """Rewrite SwiGLU on a concatenated weight, ``g, u = (x @ w.T).chunk(2, -1); silu(g) * u``
+    with ``w`` of shape ``[2 n, k]`` (the form real decoder blocks use,
+    benchmarks/muse_glimmer_block.py:41-50 of the reference), into the fused SwiGLU op on the
+    two row halves of ``w``."""
+    import operator
+
+    rewritten = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten.mul.Tensor) or len(node.args) != 2:
+            continue
+        for act, up in (node.args, node.args[::-1]):
+            found = _silu_source(act)
+            if found is None or not _is_call(up, operator.getitem):
+                continue
+            gate, chain = found
+            if not (_is_call(gate, operator.getitem) and gate.args[0] is up.args[0]
+                    and gate.args[1] == 0 and up.args[1] == 1):
+                continue
+            split = gate.args[0]
+            if not _is_call(split, aten.split.Tensor) or not _is_call(split.args[0], aten.mm.default):
+                continue
+            mm = split.args[0]
+            mv = _val(mm)
+            if mv is None or mv.dim() != 2:
+                continue
+            n2 = mv.shape[-1]
+            dim = split.args[2] if len(split.args) > 2 else 0
+            if not isinstance(n2, int) or n2 % 2 or split.args[1] != n2 // 2 or dim not in (-1, 1):
+                continue
+            x, w_t = mm.args
+            half = n2 // 2
+            claim = _claim("mm", x, w_t)
+            if claim is None or half % 8:
+                continue
+            members = set(chain) | {node, split, gate, up}
+            if not (_only_used_by(mm, {split}) and _only_used_by(split, {gate, up}) and _only_used_by(up, {node})
+                    and _only_used_by(gate, members) and all(_only_used_by(n, members) for n in chain)):
+                continue
+            dtype = claim[0]
+            with graph.inserting_before(node):
+                w = graph.call_function(aten.permute.default, (w_t, [1, 0]))
+                w.meta["val"] = _val(w_t).permute(1, 0)
+                wg = graph.call_function(aten.slice.Tensor, (w, 0, 0, half))
+                wg.meta["val"] = w.meta["val"][:half]
+                wu = graph.call_function(aten.slice.Tensor, (w, 0, half, n2))
+                wu.meta["val"] = w.meta["val"][half:]
+                new = graph.call_function(swiglu_fn_op(dtype), (x, wg, wu))
+                new.meta.update({k: v for k, v in node.meta.items() if k != "original_aten"})
+            node.replace_all_uses_with(new)
+            graph.erase_node(node)
+            rewritten += 1
+            break
+    if rewritten:
+        graph.eliminate_dead_code()
+    return rewritten
+
+
 def route_gemms(graph: torch.fx.Graph) -> int:
     """Rewrite every claimed ``aten.mm/addmm/bmm`` node of ``graph``; returns how many."""
     rewritten = 0
@@ -264,6 +440,8 @@ class AylaRoutingPass(CustomGraphPass):
 
     def __call__(self, graph: torch.fx.Graph) -> None:
         route_swiglu(graph)  # first: it consumes two mm nodes route_gemms would claim
+        route_swiglu_concat(graph)
+        route_activations(graph)
         route_gemms(graph)
         if self.previous is not None:
             self.previous(graph)
@@ -287,6 +465,9 @@ def install() -> None:
             gemm_fn_op(operation, dtype)
     for dtype in _TORCH_DTYPES:
         swiglu_fn_op(dtype)
+        for operation in ("mm", "addmm", "bmm"):
+            for activation in ("relu", "sigmoid", "silu", "gelu"):
+                gemm_fn_op(operation, dtype, DEFAULT_NAMESPACE, activation)
     current = inductor_config.post_grad_custom_post_pass
     if _installed is not None and current is _installed:
         return

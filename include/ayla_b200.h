@@ -106,6 +106,28 @@ AYLA_B200_API int ayla_b200_gemm(int op, int dtype, const void* bias, const void
                    int64_t batch, int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg,
                    void* workspace, size_t workspace_bytes, uint32_t* status, void* stream);
 
+/* Activations of ayla_b200_gemm_act. */
+#define AYLA_B200_ACT_NONE 0
+#define AYLA_B200_ACT_RELU 1
+#define AYLA_B200_ACT_SIGMOID 2
+#define AYLA_B200_ACT_SILU 3
+#define AYLA_B200_ACT_GELU 4      /* 0.5 x (1 + erf(x / sqrt 2)) */
+#define AYLA_B200_ACT_GELU_TANH 5 /* the tanh approximation */
+
+/*
+ * ayla_b200_gemm with an activation fused into the epilogue:
+ * out = act([bias +] a @ bt^T), the activation evaluated on the fp32 accumulator
+ * (after the bias) before the single rounding to the output type.  Generalises the
+ * reference's one fused-sigmoid kernel (the 4096-cube sigmoid matmul its Inductor
+ * scheduling fuses, ayla/torch_compile.py:532-547; math
+ * ayla/passes/lower_to_ptx_template.py:84-113, :296-315) to every shape, op and schedule.
+ * All other arguments as for ayla_b200_gemm.
+ */
+AYLA_B200_API int ayla_b200_gemm_act(int op, int dtype, int activation, const void* bias, const void* a,
+                                     const void* bt, void* out, int64_t batch, int64_t m, int64_t n,
+                                     int64_t k, const ayla_b200_config* cfg, void* workspace,
+                                     size_t workspace_bytes, uint32_t* status, void* stream);
+
 /*
  * Size of the scratch array built into the library for
  * ayla_b200_gemm_static_scratch: 8 MiB of device memory on every GPU that loads

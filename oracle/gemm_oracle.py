@@ -68,6 +68,24 @@ def swiglu_ref32(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> t
     return F.silu(torch.mm(xf, w_gate.float().t())) * torch.mm(xf, w_up.float().t())
 
 
+def act_ref32(activation: str, x32: torch.Tensor) -> torch.Tensor:
+    """The fused-epilogue activations on an fp32 result, before any rounding
+    (ayla/passes/lower_to_ptx_template.py:84-113 evaluates its sigmoid the same way)."""
+    if activation == "none":
+        return x32
+    if activation == "relu":
+        return torch.relu(x32)
+    if activation == "sigmoid":
+        return torch.sigmoid(x32)
+    if activation == "silu":
+        return F.silu(x32)
+    if activation == "gelu":
+        return F.gelu(x32)
+    if activation == "gelu_tanh":
+        return F.gelu(x32, approximate="tanh")
+    raise ValueError(f"unknown activation {activation}")
+
+
 def gemm_ref32(operation: str, *tensors: torch.Tensor) -> torch.Tensor:
     if operation == "mm":
         return mm_ref32(*tensors)

@@ -100,6 +100,57 @@ def test_swiglu_pattern_is_fused_and_partial_patterns_are_not():
     assert torch.ops.ayla.jit_mm_bf16_fn.default not in targets(gm)
 
 
+@pytest.mark.parametrize("activation", ["relu", "sigmoid", "silu", "gelu"])
+def test_activation_after_a_gemm_is_fused(activation):
+    import torch.nn.functional as F
+
+    act = {"relu": torch.relu, "sigmoid": torch.sigmoid, "silu": F.silu, "gelu": F.gelu}[activation]
+    mm_specs = (((64, 32), BF16, "cuda"), ((48, 32), BF16, "cuda"))
+    gm = trace(lambda a, bt: act(torch.mm(a, bt.t())), *mm_specs)
+    assert tc.route_activations(gm.graph) == 1
+    gm.graph.lint()
+    assert getattr(torch.ops.ayla, f"jit_mm_{activation}_bf16_fn").default in targets(gm)
+    leftovers = {aten.mm.default, aten.relu.default, aten.sigmoid.default, aten.erf.default, aten.exp.default}
+    assert not leftovers & set(targets(gm))
+
+    gm = trace(lambda bias, a, bt: act(torch.addmm(bias, a, bt.t())), ((48,), F16, "cuda"),
+               ((64, 32), F16, "cuda"), ((48, 32), F16, "cuda"))
+    assert tc.route_activations(gm.graph) == 1
+    assert getattr(torch.ops.ayla, f"jit_addmm_{activation}_f16_fn").default in targets(gm)
+
+    # the plain product has a second reader: nothing is fused (the GEMM itself is still claimed later)
+    gm = trace(lambda a, bt: (lambda prod: act(prod) + prod)(torch.mm(a, bt.t())), *mm_specs)
+    assert tc.route_activations(gm.graph) == 0
+    assert tc.route_gemms(gm.graph) == 1
+    # a GEMM this library would not claim keeps its activation too
+    gm = trace(lambda a, b: act(torch.mm(a, b)), ((64, 32), BF16, "cuda"), ((32, 48), BF16, "cuda"))
+    assert tc.route_activations(gm.graph) == 0
+
+
+def test_swiglu_on_a_concatenated_weight_is_fused():
+    import torch.nn.functional as F
+
+    def block(x, w):
+        gate, up = torch.mm(x, w.t()).chunk(2, dim=-1)
+        return F.silu(gate) * up
+
+    gm = trace(block, ((64, 32), BF16, "cuda"), ((96, 32), BF16, "cuda"))
+    assert tc.route_swiglu_concat(gm.graph) == 1
+    gm.graph.lint()
+    assert torch.ops.ayla.swiglu_bf16_fn.default in targets(gm) and aten.mm.default not in targets(gm)
+    # halves that are not a multiple of 8 columns, or a product that is read elsewhere, are left alone
+    gm = trace(block, ((64, 32), BF16, "cuda"), ((40, 32), BF16, "cuda"))
+    assert tc.route_swiglu_concat(gm.graph) == 0
+
+    def leaky(x, w):
+        prod = torch.mm(x, w.t())
+        gate, up = prod.chunk(2, dim=-1)
+        return F.silu(gate) * up, prod
+
+    gm = trace(leaky, ((64, 32), BF16, "cuda"), ((96, 32), BF16, "cuda"))
+    assert tc.route_swiglu_concat(gm.graph) == 0
+
+
 def test_install_is_idempotent_and_uninstall_restores():
     previous = inductor_config.post_grad_custom_post_pass
     try:
@@ -183,6 +234,49 @@ def test_torch_compile_fuses_swiglu(ayla_installed):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("activation", ["relu", "sigmoid", "silu", "gelu"])
+def test_torch_compile_fuses_activation_into_the_gemm(activation, ayla_installed):
+    import torch.nn.functional as F
+    from torch._inductor.utils import run_and_get_code
+
+    act = {"relu": torch.relu, "sigmoid": torch.sigmoid, "silu": F.silu, "gelu": F.gelu}[activation]
+    a = torch.randn(200, 256, device="cuda", dtype=torch.bfloat16)
+    bt = (torch.randn(264, 256, device="cuda") * 256 ** -0.5).bfloat16()
+    bias = torch.randn(264, device="cuda", dtype=torch.bfloat16)
+
+    def layer(a, bt, bias):
+        return act(torch.addmm(bias, a, bt.T))
+
+    with torch.no_grad(), inductor_config.patch(force_disable_caches=True):
+        actual, code = run_and_get_code(torch.compile(layer, fullgraph=True, dynamic=False), a, bt, bias)
+    expected = act(torch.addmm(bias.float(), a.float(), bt.float().T)).bfloat16()
+    torch.testing.assert_close(actual, expected, atol=0.05, rtol=0.02)
+    assert any(f"jit_addmm_{activation}_bf16" in source for source in code)
+    assert not any("triton" in source and "sigmoid" in source for source in code)
+
+
+@pytest.mark.gpu
+def test_torch_compile_fuses_swiglu_on_a_concatenated_weight(ayla_installed):
+    import torch.nn.functional as F
+    from torch._inductor.utils import run_and_get_code
+
+    x = torch.randn(200, 256, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(528, 256, device="cuda") * 256 ** -0.5).bfloat16()
+
+    def mlp(x, w):
+        gate, up = torch.mm(x, w.T).chunk(2, dim=-1)
+        return F.silu(gate) * up
+
+    with torch.no_grad(), inductor_config.patch(force_disable_caches=True):
+        actual, code = run_and_get_code(torch.compile(mlp, fullgraph=True, dynamic=False), x, w)
+    both = x.float() @ w.float().T
+    expected = (F.silu(both[:, :264]) * both[:, 264:]).bfloat16()
+    torch.testing.assert_close(actual, expected, atol=0.05, rtol=0.02)
+    assert any("swiglu_bf16" in source for source in code)
+    assert not any("jit_mm_" in source for source in code)
+
+
+@pytest.mark.gpu
 def test_torch_compile_declines_cpu_and_plain_layout(ayla_installed):
     from torch._inductor.utils import run_and_get_code
 
@@ -192,3 +286,14 @@ def test_torch_compile_declines_cpu_and_plain_layout(ayla_installed):
         actual, code = run_and_get_code(torch.compile(lambda x, y: torch.mm(x, y), dynamic=False), a, b)
     torch.testing.assert_close(actual, a @ b, atol=0.125, rtol=0.02)
     assert not any("jit_mm_" in source for source in code)
+
+
+@pytest.mark.gpu
+def test_whole_graph_driver_routes_a_decoder_block():
+    from ayla_b200.bench_torch_compile import run
+
+    row = run(tokens=64, layers=1, hidden=256, ffn=512, heads=4, kv_heads=2)
+    counts = row["routed_calls_in_generated_code"]
+    assert counts["jit_mm_bf16_fn"] >= 3 and counts["swiglu_bf16_fn"] >= 1
+    assert row["fro_rel_between_arms"] < 2e-2
+    assert row["stock_inductor_ms"] > 0 and row["ayla_b200_ms"] > 0
