@@ -39,6 +39,8 @@ BASELINE_SHAPES = [
     ("bmm", "bfloat16", 8, 2048, 128, 2048),
     ("mm", "bfloat16", 1, 4096, 4096, 32768),
 ]
+# Projections of an 8B-class decoder that the sweep does not cover (fused QKV, concatenated gate/up).
+DECODER_SHAPES = [("mm", "bfloat16", 1, m, n, 4096) for n in (6144, 28672) for m in (8, 64, 512, 4096)]
 SWEEP_SHAPES = [("mm", "bfloat16", 1, m, n, k) for n, k in SWEEP_NK for m in SWEEP_M]
 
 
@@ -222,7 +224,7 @@ def emit_table(results_path: Path, table_path: Path, keep: int = 3) -> None:
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--out", default="gpurun_out/autotune.json")
-    parser.add_argument("--shapes", default="all", choices=["all", "baseline", "sweep"])
+    parser.add_argument("--shapes", default="all", choices=["all", "baseline", "sweep", "decoder"])
     parser.add_argument("--emit", default=None, help="write the schedule table to this path instead of measuring")
     args = parser.parse_args()
     out = Path(args.out)
@@ -235,6 +237,8 @@ def main() -> None:
         shapes += BASELINE_SHAPES
     if args.shapes in ("all", "sweep"):
         shapes += SWEEP_SHAPES
+    if args.shapes in ("all", "decoder"):
+        shapes += DECODER_SHAPES
     measure(shapes, out)
 
 

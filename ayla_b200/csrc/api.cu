@@ -500,8 +500,24 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   const KernelEntry& e = *plan.kernel;
   LaunchArgs la;
   memset(&la, 0, sizeof(la));
-  const int b_box_rows = (e.epilogue == EPI_SWIGLU) ? 128 : e.tile_n / e.cta_group;
-  int rc = encode_map(&la.tm_a, pr.row_operand, pr.k, pr.rows, pr.batch, 64, plan.tile_rows, 1);
+  int b_box_rows = (e.epilogue == EPI_SWIGLU) ? 128 : e.tile_n / e.cta_group;
+  int b_stage_rows = e.tile_n / e.cta_group;  // rows of the column operand one CTA receives per stage
+  int a_box_rows = plan.tile_rows;
+  // An operand that fits in a single tile is loaded with a box of just its own rows (rounded
+  // up to the 8-row swizzle atom): rows of the box that lie outside the tensor are zero-filled
+  // by TMA at a cost comparable to real rows, and a GEMM with a handful of rows would spend
+  // most of its load time on them.  The shared-memory rows the smaller box leaves untouched
+  // feed only accumulator rows / columns that are never stored.
+  if (e.cta_group == 1) {
+    const int rows8 = static_cast<int>(ceil_div(pr.rows, 8) * 8);
+    const int cols8 = static_cast<int>(ceil_div(pr.cols, 8) * 8);
+    if (plan.m_tiles == 1 && rows8 < a_box_rows) a_box_rows = rows8;
+    if (plan.n_tiles == 1 && e.epilogue != EPI_SWIGLU && plan.narrow_from_tile == 0x7FFFFFFF && cols8 < b_box_rows) {
+      b_box_rows = cols8;
+      b_stage_rows = cols8;
+    }
+  }
+  int rc = encode_map(&la.tm_a, pr.row_operand, pr.k, pr.rows, pr.batch, 64, a_box_rows, 1);
   if (rc) return rc;
   rc = encode_map(&la.tm_b, pr.col_operand, pr.k, pr.cols, pr.batch, 64, b_box_rows, 1);
   if (rc) return rc;
@@ -553,7 +569,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.act = activation;
   // One stage receives this CTA's rows of the row operand and its share of the column
   // operand; the leader of a pair counts both CTAs' bytes.
-  p.stage_tx = static_cast<uint32_t>((plan.tile_rows + e.tile_n / e.cta_group) * 128 * e.cta_group);
+  p.stage_tx = static_cast<uint32_t>((a_box_rows + b_stage_rows) * 128 * e.cta_group);
   if (plan.slabs > 0) {
     const size_t need = workspace_bytes_for(plan);
     if (workspace == nullptr || workspace_bytes < need) {

@@ -102,6 +102,25 @@ def _seed(captured: dict[str, object], operation: str, dtype: str, m: int, n: in
     )
 
 
+_SM_COUNT = 148
+
+
+def _waves(config: dict[str, object], batch: int, m: int, n: int) -> int:
+    """Passes of the persistent grid a schedule needs on this shape (whole CTAs or clusters at
+    a time).  A schedule measured at one wave is a poor guess for a shape where it needs two."""
+    pair = int(config["cta_group"])
+    rows, cols = (n, m) if config["swap_ab"] else (m, n)
+    tile_rows = int(config["tile_rows"]) or 128
+    row_tiles = -(-rows // (tile_rows if config["swap_ab"] else 128 * pair))
+    tiles = batch * row_tiles * -(-cols // int(config["tile_n"]))
+    split = int(config["split_k"])
+    if config["cluster_split"]:
+        cluster = split * pair
+        return -(-tiles // max(1, _SM_COUNT // cluster))
+    units = tiles * (1 if config["split_tail"] else split)
+    return -(-units // (_SM_COUNT // pair))
+
+
 def measured_gemm_configs(operation: str, dtype: str, m: int, n: int, k: int,
                           batch: int = 1) -> tuple[dict[str, object], ...]:
     """All schedules measured on exactly this shape, winner first, as fresh copies."""
@@ -133,8 +152,10 @@ def select_gemm_schedule(operation: str, dtype: str, m: int, n: int, k: int,
         if distance(shape) > _MAX_TRANSFER_DISTANCE:
             break
         for index in table[shape]:
-            seed = _seed({**_DEFAULTS, **CONFIGS[index]}, operation, dtype, m, n, k, batch, shape,
-                         exact=shape == query)
+            captured = {**_DEFAULTS, **CONFIGS[index]}
+            if shape != query and _waves(captured, batch, m, n) > _waves(captured, shape[0], shape[1], shape[2]):
+                continue  # it would no longer fit the number of waves it was measured at
+            seed = _seed(captured, operation, dtype, m, n, k, batch, shape, exact=shape == query)
             if seed is not None:
                 return seed
     return _fallback_schedule(operation, dtype, m, n, k, batch)
