@@ -538,6 +538,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t idesc = p.idesc;
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
+#ifdef AYLA_B200_TRACE
+      bool first_operands_stamped = false;
+#endif
       AYLA_TRACE_BEGIN
       UnitCursor<T> cursor(p, first_unit, unit_stride, 0, csk_rank);
       WorkUnit w;
@@ -550,7 +553,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL))
 #ifdef AYLA_B200_TRACE
-          if (stamps != nullptr && lane == 0 && stamps[2] == 0) stamps[2] = static_cast<long long>(global_timer_ns());
+          if (stamps != nullptr && lane == 0 && !first_operands_stamped) {
+            stamps[2] = static_cast<long long>(global_timer_ns());
+            first_operands_stamped = true;
+          }
 #endif
           tc_fence_after_sync();
           if (issuer) {
