@@ -1,7 +1,7 @@
 """Measure candidate schedules per shape on a B200 and regenerate the schedule table.
 
-    python -m ayla_b200.autotune --out gpurun_out/autotune.json            # measure (resumable)
-    python -m ayla_b200.autotune --out gpurun_out/autotune.json --emit ayla_b200/gemm_schedule_table.py
+    python -m ayla_b200.autotune --out results/autotune.json            # measure (resumable)
+    python -m ayla_b200.autotune --out results/autotune.json --emit ayla_b200/gemm_schedule_table.py
 
 The sweep mirrors how the reference's table was produced (per-shape sweeps whose winners are
 stored first, ayla/gemm_schedule_table.py:1-12) and its harness' resume behaviour: results are
@@ -25,7 +25,7 @@ from .suite import SWEEP_M, SWEEP_NK, _copies, time_interleaved
 MAX_WORKSPACE = 512 << 20
 SM_COUNT = 148
 
-BASELINE_SHAPES = [
+HEADLINE_SHAPES = [
     ("mm", "bfloat16", 1, 4096, 4096, 4096),
     ("mm", "float16", 1, 4096, 4096, 4096),
     ("mm", "bfloat16", 1, 8192, 8192, 8192),
@@ -223,7 +223,7 @@ def emit_table(results_path: Path, table_path: Path, keep: int = 3) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--out", default="gpurun_out/autotune.json")
+    parser.add_argument("--out", default="results/autotune.json")
     parser.add_argument("--shapes", default="all", choices=["all", "baseline", "sweep", "decoder"])
     parser.add_argument("--emit", default=None, help="write the schedule table to this path instead of measuring")
     args = parser.parse_args()
@@ -234,7 +234,7 @@ def main() -> None:
     out.parent.mkdir(parents=True, exist_ok=True)
     shapes = []
     if args.shapes in ("all", "baseline"):
-        shapes += BASELINE_SHAPES
+        shapes += HEADLINE_SHAPES
     if args.shapes in ("all", "sweep"):
         shapes += SWEEP_SHAPES
     if args.shapes in ("all", "decoder"):

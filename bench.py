@@ -20,7 +20,8 @@ no CPU kernel of its own, its tests define the result as PyTorch's fp32 matmul
 (tests/gemm_collection/test_correctness.py:419), which is what the oracle restates.
 
 ``--suite`` additionally measures every benchmark config (addmm, split-K, bmm, SwiGLU,
-the dynamic-M sweep) against cuBLAS and writes ``gpurun_out/suite.json``.
+the dynamic-M sweep) against cuBLAS and writes the rows to ``--suite-out`` (default
+``results/suite.json``).
 
 With ``--gpus N`` (launched under torchrun, one rank per GPU) every rank runs the same
 workload on its own GPU (the 4096^3 GEMM does not shard usefully: replicas, weak
@@ -258,6 +259,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--suite", action="store_true")
+    parser.add_argument("--suite-out", default="results/suite.json")
     parser.add_argument("--no-extra", action="store_true")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -398,9 +400,10 @@ def main() -> None:
     if args.suite and world == 1:
         from ayla_b200.suite import run_suite
 
-        os.makedirs(ROOT / "gpurun_out", exist_ok=True)
         rows = run_suite(peaks)
-        (ROOT / "gpurun_out" / "suite.json").write_text(json.dumps(rows, indent=1))
+        suite_out = Path(args.suite_out)
+        suite_out.parent.mkdir(parents=True, exist_ok=True)
+        suite_out.write_text(json.dumps(rows, indent=1))
     print(json.dumps(line), flush=True)
 
 

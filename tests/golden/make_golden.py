@@ -2,7 +2,7 @@
 
 Run from the repository root in a container that holds the reference checkout:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [--reference /path/to/ayla]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference /path/to/ayla
 
 Two files are written:
 
@@ -173,7 +173,7 @@ def make_reference_api(reference: Path) -> None:
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     args = parser.parse_args()
     make_vectors()
     make_reference_api(Path(args.reference))
