@@ -44,12 +44,17 @@ struct Registry {
     append_variants_cg2(entries, &count);
     append_variants_trans(entries, &count);
     append_variants_swiglu(entries, &count);
+    base_count = count;
+    append_variants_act_cg1(entries, &count);
+    append_variants_act_cg2(entries, &count);
+    append_variants_act_trans(entries, &count);
   }
-  const KernelEntry* find(int tile_n, int cta_group, int epilogue, int transposed) const {
+  int base_count = 0;  // the variants without the activation epilogue come first
+  const KernelEntry* find(int tile_n, int cta_group, int epilogue, int transposed, int activation = 0) const {
     for (int i = 0; i < count; ++i) {
       const KernelEntry& e = entries[i];
       if (e.tile_n == tile_n && e.cta_group == cta_group && e.epilogue == epilogue &&
-          e.transposed_out == transposed) {
+          e.transposed_out == transposed && e.activation == activation) {
         return &e;
       }
     }
@@ -259,10 +264,10 @@ constexpr size_t kCounterBytes = static_cast<size_t>(kMaxSplitKTiles) * 4;
 
 // Fills `plan` for a validated config.  `epilogue` is one of EPI_*.
 int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t rows, int64_t cols,
-              int64_t k, int sm_count, Plan* plan) {
+              int64_t k, int sm_count, Plan* plan, int activation = 0) {
   const int transposed = c.swap_ab ? 1 : 0;
   const int tile_n = (epilogue == EPI_SWIGLU) ? 256 : c.tile_n;
-  const KernelEntry* e = registry().find(tile_n, c.cta_group, epilogue, transposed);
+  const KernelEntry* e = registry().find(tile_n, c.cta_group, epilogue, transposed, activation != 0 ? 1 : 0);
   if (e == nullptr) {
     return fail(AYLA_B200_E_UNSUPPORTED, "no kernel variant tile_n=%d cta_group=%d epilogue=%d swap=%d",
                 tile_n, c.cta_group, epilogue, transposed);
@@ -789,7 +794,7 @@ int ayla_b200_gemm_act(int op, int dtype, int activation, const void* bias, cons
   }
   const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
   Plan plan;
-  rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan);
+  rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan, activation);
   if (rc) return rc;
   return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, workspace,
                      workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream), activation);
@@ -897,12 +902,14 @@ int ayla_b200_swiglu(int dtype, const void* x, const void* w_gate, const void* w
                      status, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int ayla_b200_kernel_count(void) { return registry().count; }
+// The listing covers the variants without the activation epilogue; each of them except the
+// SwiGLU pair exists a second time with it.
+int ayla_b200_kernel_count(void) { return registry().base_count; }
 
 int ayla_b200_kernel_info(int i, int32_t* tile_n, int32_t* cta_group, int32_t* epilogue,
                           int32_t* transposed_out, int32_t* stages, int32_t* smem_bytes) {
   const Registry& reg = registry();
-  if (i < 0 || i >= reg.count) return fail(AYLA_B200_E_INVALID, "variant index %d out of range", i);
+  if (i < 0 || i >= reg.base_count) return fail(AYLA_B200_E_INVALID, "variant index %d out of range", i);
   const KernelEntry& e = reg.entries[i];
   if (tile_n) *tile_n = e.tile_n;
   if (cta_group) *cta_group = e.cta_group;

@@ -96,8 +96,12 @@ struct KernelParams {
 #define AYLA_TRACE_END(slot)
 #endif
 
-template <int BN_, int CTA_GROUP_, int EPI_, bool TRANS_OUT_, int STAGES_>
+template <int BN_, int CTA_GROUP_, int EPI_, bool TRANS_OUT_, int STAGES_, bool ACT_ = false>
 struct GemmTraits {
+  // ACT: the epilogue applies the activation named in the launch parameters.  A separate set of
+  // instantiations, so that the plain kernels carry none of that code (compiled in as a run-time
+  // branch it cost the output-bound bmm 5 %).
+  static constexpr bool ACT = ACT_;
   static constexpr int BN = BN_;                // MMA N (accumulator columns)
   static constexpr int CTA_GROUP = CTA_GROUP_;
   static constexpr int EPI = EPI_;
@@ -613,7 +617,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int epi_tid = (warp - 2) * 32 + lane;      // 0..255
     const int row_in_tile = q * 32 + lane;
     const int is_bf16 = p.is_bf16;
-    const int act = p.act;
+    const int act = T::ACT ? p.act : static_cast<int>(ACT_NONE);
     uint8_t* my_store = smem_store + (warp - 2) * T::STORE_BUF_BYTES;
     uint32_t acc = 0, acc_phase = 0;
     uint32_t bias_buf = 0;
