@@ -10,9 +10,9 @@
 //   warp 0      TMA producer  : global -> shared ring of STAGES (A 128x64, B BNx64) slabs
 //   warp 1      MMA issuer    : tcgen05.mma from shared into a TMEM accumulator;
 //                               also owns the TMEM allocation
-//   warps 2..9  epilogue      : TMEM -> registers -> (bias | SiLU*up) -> round ->
+//   warps 2..9  epilogue      : TMEM -> registers -> (bias | activation | SiLU*up) -> round ->
 //                               swizzled shared -> TMA store   (or direct stores for the
-//                               transposed / split-K forms)
+//                               transposed form and narrow cluster slices)
 // The accumulator is double buffered in TMEM so the epilogue of one tile runs
 // under the main loop of the next.  CTAs are persistent and walk a static,
 // M-grouped raster over (batch, m-tile, n-tile, k-split) work units.
@@ -20,6 +20,10 @@
 // CTA_GROUP == 2 pairs two CTAs (cluster of 2) on one 256-row tile: each CTA
 // loads its own 128 rows of A and its own half of the B tile with ordinary TMA
 // loads, the leader CTA issues tcgen05.mma.cta_group::2 for both.
+//
+// Launch overlap: the kernel runs its set-up, then executes griddepcontrol.wait before its first
+// global access and griddepcontrol.launch_dependents right after, so that back-to-back launches
+// issued with programmatic stream serialisation overlap set-up with the previous kernel's drain.
 #pragma once
 
 #include <cuda_bf16.h>

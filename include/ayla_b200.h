@@ -214,7 +214,11 @@ AYLA_B200_API size_t ayla_b200_workspace_counter_bytes(const ayla_b200_config* c
 AYLA_B200_API int ayla_b200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
                                     size_t width_bytes, size_t rows, void* stream);
 
-/* Number of compiled kernel variants, and a description of variant i. */
+/*
+ * Number of compiled kernel variants, and a description of variant i.  The listing covers the
+ * variants without the activation epilogue; every one of them except the two SwiGLU kernels
+ * exists a second time with it (used by ayla_b200_gemm_act).
+ */
 AYLA_B200_API int ayla_b200_kernel_count(void);
 AYLA_B200_API int ayla_b200_kernel_info(int i, int32_t* tile_n, int32_t* cta_group, int32_t* epilogue,
                           int32_t* transposed_out, int32_t* stages, int32_t* smem_bytes);
