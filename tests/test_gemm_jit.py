@@ -117,3 +117,34 @@ def test_meta_dispatch_allocates_nothing_and_returns_none():
         if operation == "addmm":
             args.insert(0, torch.empty(16, dtype=torch.bfloat16, device="meta"))
         assert gemm_op(operation, "bfloat16")(*args) is None
+
+
+def test_transferred_schedules_keep_their_wave_count():
+    """A schedule measured on a neighbouring shape is not used where it would need more passes of
+    the persistent grid than on the shape it was measured on (a fused QKV projection, n = 6144,
+    next to the measured n = 4096 shapes)."""
+    from ayla_b200.gemm_jit import _waves
+
+    for m in (8, 64, 512, 2048):
+        seed = select_gemm_schedule("mm", "bfloat16", m, 6144 + 1024, 4096)  # n = 7168: not in the table
+        assert seed is not None and seed.builder_config is not None
+        config = {**seed.captured_config}
+        if seed.source_shape is not None:
+            source = (1, *seed.source_shape)
+            assert _waves(config, 1, m, 7168) <= _waves(config, source[0], source[1], source[2])
+        assert _lib.config_valid(_lib.Config.from_dict(seed.builder_config), "mm", "bfloat16", 1, m, 7168, 4096)
+
+
+def test_activation_ops_are_registered_with_the_plain_ops_signature():
+    from ayla_b200.gemm_jit import ACTIVATIONS, gemm_act_op
+
+    assert ACTIVATIONS[0] == "none" and gemm_act_op("mm", "none", "float16") is gemm_op("mm", "float16")
+    op = gemm_act_op("addmm", "relu", "float16")
+    assert str(op._schema) == ("ayla::jit_addmm_relu_f16(Tensor arg0, Tensor arg1, Tensor arg2, Tensor(a3!) arg3) -> ()")
+    bias = torch.empty(16, dtype=torch.float16, device="meta")
+    a = torch.empty(8, 32, dtype=torch.float16, device="meta")
+    bt = torch.empty(16, 32, dtype=torch.float16, device="meta")
+    out = torch.empty(8, 16, dtype=torch.float16, device="meta")
+    assert op(bias, a, bt, out) is None
+    with pytest.raises(ValueError, match="unsupported GEMM activation"):
+        gemm_act_op("mm", "tanh", "float16")
