@@ -449,6 +449,15 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
       }
     }
     c->group_m = 1;
+    if (c->split_k == 1 && m > 16) {
+      // No room to split K (bt alone fills the SMs): with a few dozen rows of `a` the plain
+      // row-major 128-wide tile, its `a` box trimmed to the rows that exist, measures 1.2-1.3x
+      // faster than the swapped form (M = 32, 64 at N = 14336).
+      c->swap_ab = 0;
+      c->tile_n = (batch * ceil_div(n, 128) <= static_cast<int64_t>(sm_count)) ? 128 : 256;  // one wave if it fits
+      c->group_m = 8;
+      c->split_tail = 2;
+    }
     return;
   }
   // Row-major form: pick (tile width, CTA pairing, k-split) by a small cost model fitted to
@@ -479,11 +488,14 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
           tail = 2;
         }
       }
-      // Unpaired tiles split K across a cluster (cheap exchange through distributed shared
-      // memory, cluster sizes 2/4/8); paired tiles go through the workspace, where the last
+      // Up to four CTAs (two pairs) split K across a cluster (cheap exchange through
+      // distributed shared memory); deeper splits go through the workspace, where the last
       // arriver sums `split` partial tiles one after the other.
-      const bool cluster = split > 1 && sh.cta_group == 1 && split <= 4;
-      const double fixup = split == 1 ? 0.0 : (cluster ? 3.0 + 0.1 * split * (sh.tile_n / 64.0)
+      const bool cluster = split > 1 && split * sh.cta_group <= 4;
+      // Cluster exchange: two cluster barriers plus the partial columns each CTA sends,
+      // 128 x tile_n x 4 bytes x (split - 1) / split, at about 16 KB per cost unit.
+      const double exchange_kb = 0.5 * sh.tile_n * (split - 1) / split;
+      const double fixup = split == 1 ? 0.0 : (cluster ? 2.5 + exchange_kb / 16.0
                                                        : 4.0 + 0.9 * split * (sh.tile_n / 64.0));
       const double cost = waves * tile_cost / split + fixup + launch_cost;
       if (cost < best_cost) {

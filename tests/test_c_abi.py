@@ -81,8 +81,16 @@ def test_default_schedules_for_the_benchmark_shapes():
     assert (whole.split_k, whole.split_tail) == (1, 0)
     decode = _lib.default_config("mm", "bfloat16", 1, 1, 4096, 4096)
     assert decode.swap_ab == 1 and decode.tile_n == 16 and decode.split_k >= 2
+    # 112 tiles of bt leave no room to split K: a few dozen rows of `a` go through the plain 128-wide
+    # tile (its `a` box trimmed), a handful stay on the swapped form
     m64 = _lib.default_config("mm", "bfloat16", 1, 64, 14336, 4096)
-    assert m64.swap_ab == 1 and m64.tile_n == 64
+    assert (m64.swap_ab, m64.tile_n, m64.split_k) == (0, 128, 1)
+    m8 = _lib.default_config("mm", "bfloat16", 1, 8, 14336, 4096)
+    assert (m8.swap_ab, m8.tile_n) == (1, 16)
+    m64_k = _lib.default_config("mm", "bfloat16", 1, 64, 4096, 4096)  # 32 tiles: K split over a cluster of 4
+    assert (m64_k.swap_ab, m64_k.tile_n, m64_k.split_k, m64_k.cluster_split) == (1, 64, 4, 1)
+    m256 = _lib.default_config("mm", "bfloat16", 1, 256, 4096, 4096)  # pairs, K split over two pairs
+    assert (m256.tile_n, m256.cta_group, m256.split_k, m256.cluster_split) == (128, 2, 2, 1)
     deep = _lib.default_config("addmm", "bfloat16", 1, 256, 1024, 16384)
     assert deep.swap_ab == 0 and deep.split_k > 1
     for cfg, shape in ((big, (1, 4096, 4096, 4096)), (decode, (1, 1, 4096, 4096)),
