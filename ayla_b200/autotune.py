@@ -146,7 +146,7 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
     refine = {}
     for name, _ in ranked[:2]:
         base = configs[name]
-        tweaks = [dict(l2_hint_a=1), dict(l2_hint_b=1), dict(l2_hint_a=2), dict(l2_hint_b=2)]
+        tweaks = [dict(l2_hint_a=a, l2_hint_b=b) for a in (0, 1, 2) for b in (0, 1, 2) if a or b]
         if not base.get("swap_ab"):
             tweaks += [dict(group_m=g) for g in (2, 4, 16) if g != base.get("group_m")]
         for j, tweak in enumerate(tweaks):
