@@ -169,6 +169,17 @@ def max_over_ranks(value: float, world: int) -> float:
     return float(t.item())
 
 
+def max_over_ranks_list(values: list[float], world: int) -> list[float]:
+    """Element-wise maximum over ranks, so that every rank makes the same choice from the list."""
+    if world == 1:
+        return values
+    import torch.distributed as dist
+
+    t = torch.tensor(values, dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
 def barrier(world: int):
     if world > 1:
         import torch.distributed as dist
@@ -287,6 +298,31 @@ def main() -> None:
     stream = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(1, dtype=torch.int32, device=device)
 
+    # The table ranks schedules by short graph-replayed bursts; this loop runs for seconds under the
+    # power cap, where the L2 eviction hints that keep operands resident can rank differently.  So,
+    # as part of the warm-up, each schedule measured for this shape runs 300 back-to-back launches
+    # and the fastest is the one timed (reported in config.schedule).
+    from ayla_b200.gemm_jit import measured_gemm_configs
+
+    candidates = [_lib.Config.from_dict({key: c[key] for key in _lib.Config.FIELDS}) for c in
+                  measured_gemm_configs("mm", "bfloat16", M, N, K)]
+    schedule_choice = "the library's schedule for this shape"
+    if len(candidates) > 1:
+        def trial(candidate):
+            def run(i):
+                a, bt, out = sets[i % len(sets)]
+                _lib.gemm("mm", "bfloat16", 0, a.data_ptr(), bt.data_ptr(), out.data_ptr(), 1, M, N, K, candidate,
+                          0, 0, status.data_ptr(), stream)
+            for i in range(20):
+                run(i)
+            return cuda_time_ms(run, 300)
+
+        trials = [trial(c) for c in candidates]
+        trials = max_over_ranks_list(trials, world)
+        cfg = candidates[min(range(len(trials)), key=trials.__getitem__)]
+        schedule_choice = (f"fastest of the {len(candidates)} schedules measured for this shape over 300 warm "
+                           f"launches each ({', '.join(f'{t * 1e3:.1f}' for t in trials)} us)")
+
     def step(i):
         a, bt, out = sets[i % len(sets)]
         _lib.gemm("mm", "bfloat16", 0, a.data_ptr(), bt.data_ptr(), out.data_ptr(), 1, M, N, K, cfg, 0, 0,
@@ -386,7 +422,7 @@ def main() -> None:
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "schedule": cfg.to_dict(),
+        "config": {"workload": WORKLOAD, "schedule": cfg.to_dict(), "schedule_choice": schedule_choice,
                    "l2": f"launches rotate over {len(sets)} operand sets, {len(sets) * ALGO_BYTES / 1e6:.0f} MB > 126 MB L2",
                    "parallelism": "replicas" if world > 1 else "1 GPU",
                    "inputs": "a, bt ~ N(0,1) from seed 0 (set 0); fp32 accumulate, bf16 out"},
