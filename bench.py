@@ -227,6 +227,12 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1 for its workers; this arm runs on rank 0 alone and may
+    # use every host core the process is allowed.
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        torch.set_num_threads(os.cpu_count() or 1)
     from oracle import gemm_oracle as O
 
     _, (a0, bt0) = O.make_inputs("C1", "bfloat16")
