@@ -41,6 +41,9 @@ HEADLINE_SHAPES = [
 ]
 # Projections of an 8B-class decoder that the sweep does not cover (fused QKV, concatenated gate/up).
 DECODER_SHAPES = [("mm", "bfloat16", 1, m, n, 4096) for n in (6144, 28672) for m in (8, 64, 512, 4096)]
+# Larger models: hidden 8192, FFN 28672 (70B-class layer shapes), decode and prefill row counts.
+LARGE_SHAPES = [("mm", "bfloat16", 1, m, n, k) for (n, k) in ((8192, 8192), (10240, 8192), (28672, 8192), (8192, 28672))
+                for m in (8, 64, 512, 4096)]
 SWEEP_SHAPES = [("mm", "bfloat16", 1, m, n, k) for n, k in SWEEP_NK for m in SWEEP_M]
 
 
@@ -244,7 +247,7 @@ def emit_table(results_path: Path, table_path: Path, keep: int = 3) -> None:
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--out", default="results/autotune.json")
-    parser.add_argument("--shapes", default="all", choices=["all", "baseline", "sweep", "decoder"])
+    parser.add_argument("--shapes", default="all", choices=["all", "baseline", "sweep", "decoder", "large"])
     parser.add_argument("--emit", default=None, help="write the schedule table to this path instead of measuring")
     args = parser.parse_args()
     out = Path(args.out)
@@ -259,6 +262,8 @@ def main() -> None:
         shapes += SWEEP_SHAPES
     if args.shapes in ("all", "decoder"):
         shapes += DECODER_SHAPES
+    if args.shapes in ("all", "large"):
+        shapes += LARGE_SHAPES
     measure(shapes, out)
 
 

@@ -140,7 +140,9 @@ def select_gemm_schedule(operation: str, dtype: str, m: int, n: int, k: int,
         return None
     if dtype not in _SHORT_DTYPES:
         return None
-    table = SCHEDULES.get((operation, dtype), {})
+    # fp16 and bf16 run the same kernels at the same speed: a shape measured only in one serves the other
+    other = "float16" if dtype == "bfloat16" else "bfloat16"
+    table = {**SCHEDULES.get((operation, other), {}), **SCHEDULES.get((operation, dtype), {})}
     if not _shape_supported(m, n, k, batch):
         return None
     query = (batch, m, n, k)
@@ -157,6 +159,10 @@ def select_gemm_schedule(operation: str, dtype: str, m: int, n: int, k: int,
                 continue  # it would no longer fit the number of waves it was measured at
             seed = _seed(captured, operation, dtype, m, n, k, batch, shape, exact=shape == query)
             if seed is not None:
+                if shape not in SCHEDULES.get((operation, dtype), {}):
+                    seed = GemmScheduleSeed(seed.captured_config, seed.builder_config,
+                                            (*seed.adaptations, f"measured in {other}"), seed.source_shape,
+                                            seed.source_percentage_of_torch)
                 return seed
     return _fallback_schedule(operation, dtype, m, n, k, batch)
 
