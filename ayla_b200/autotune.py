@@ -7,7 +7,9 @@ The sweep mirrors how the reference's table was produced (per-shape sweeps whose
 stored first, ayla/gemm_schedule_table.py:1-12) and its harness' resume behaviour: results are
 rewritten atomically after every shape and finished shapes are skipped on a re-run
 (benchmarks/oss_gemm_corpus.py:418-442, benchmarks/benchmark_oss_pytorch_gemm_shapes.py:294-318).
-Timing protocol: see :mod:`ayla_b200.suite`.
+The results file has to be present where the sweep runs for finished shapes to be skipped and kept:
+a run that starts without it writes only the shapes it measured.  Timing protocol: see
+:mod:`ayla_b200.suite`.
 """
 
 from __future__ import annotations
