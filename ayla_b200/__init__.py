@@ -17,6 +17,7 @@ and are reached through the C ABI declared in ``include/ayla_b200.h``.
 from .gemm_jit import (
     ACTIVATIONS,
     GemmScheduleSeed,
+    gemm_act_mul_op,
     gemm_act_op,
     gemm_jit_compiler,
     gemm_op,
@@ -33,6 +34,7 @@ __all__ = [
     "GemmScheduleSeed",
     "OperandKind",
     "TensorSpec",
+    "gemm_act_mul_op",
     "gemm_act_op",
     "gemm_jit_compiler",
     "gemm_op",

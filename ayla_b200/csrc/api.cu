@@ -517,7 +517,7 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
 int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, int is_bf16,
                 const void* bias, const void* b2_operand, void* out, int64_t out_rows,
                 int64_t out_cols, void* workspace, size_t workspace_bytes, uint32_t* status,
-                cudaStream_t stream, int activation = 0) {
+                cudaStream_t stream, int activation = 0, const void* mul = nullptr) {
   const KernelEntry& e = *plan.kernel;
   LaunchArgs la;
   memset(&la, 0, sizeof(la));
@@ -588,6 +588,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.l2_prefetch = c.l2_prefetch;
   p.tile_rows = plan.tile_rows;
   p.act = activation;
+  p.mul = mul;
   // One stage receives this CTA's rows of the row operand and its share of the column
   // operand; the leader of a pair counts both CTAs' bytes.
   p.stage_tx = static_cast<uint32_t>((a_box_rows + b_stage_rows) * 128 * e.cta_group);
@@ -766,6 +767,17 @@ int ayla_b200_gemm_act(int op, int dtype, int activation, const void* bias, cons
                        void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
                        const ayla_b200_config* cfg, void* workspace, size_t workspace_bytes,
                        uint32_t* status, void* stream) {
+  return ayla_b200_gemm_act_mul(op, dtype, activation, bias, a, bt, nullptr, out, batch, m, n, k, cfg, workspace,
+                                workspace_bytes, status, stream);
+}
+
+int ayla_b200_gemm_act_mul(int op, int dtype, int activation, const void* bias, const void* a, const void* bt,
+                           const void* mul, void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
+                           const ayla_b200_config* cfg, void* workspace, size_t workspace_bytes,
+                           uint32_t* status, void* stream) {
+  if (mul != nullptr && !aligned16(mul)) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "mul must be 16-byte aligned");
+  }
   int rc = check_shape(op, dtype, batch, m, n, k);
   if (rc) return rc;
   if (activation < AYLA_B200_ACT_NONE || activation > AYLA_B200_ACT_GELU_TANH) {
@@ -810,10 +822,10 @@ int ayla_b200_gemm_act(int op, int dtype, int activation, const void* bias, cons
   }
   const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
   Plan plan;
-  rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan, activation);
+  rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan, (activation != 0 || mul != nullptr) ? 1 : 0);
   if (rc) return rc;
   return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, workspace,
-                     workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream), activation);
+                     workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream), activation, mul);
 }
 
 int ayla_b200_gemm_static_scratch(int op, int dtype, const void* bias, const void* a, const void* bt,

@@ -77,6 +77,7 @@ struct KernelParams {
   long long* trace;   // per-CTA cycle counters, written only by AYLA_B200_TRACE builds
   int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
   int l2_prefetch;    // k-blocks the producer prefetches into L2 ahead of its shared-memory loads
+  const void* mul;    // optional gate, same shape and layout as `out`: out = act(...) * mul (activation variants)
   int act;            // activation applied to the fp32 result (after the bias) before rounding: ACT_*
   int tile_rows;      // swapped form: rows of the row operand per tile (8..128); 128 otherwise
   uint32_t stage_tx;  // bytes one ring stage receives (both CTAs of a pair together)
@@ -310,6 +311,11 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
   }
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float2 unpack2(uint32_t v, int is_bf16) {
+  if (is_bf16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
 
 __device__ __forceinline__ float load_elem(const void* base, long long i, int is_bf16) {
@@ -676,6 +682,41 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       };
 
+      // Gate (activation variants, row-major output): multiply this thread's 32 values of chunk
+      // `c32` by the matching elements of `mul`, which has the shape and layout of `out`.
+      auto gate_chunk = [&](float (&v)[32], int c32) {
+        if constexpr (T::ACT && !T::TRANS_OUT) {
+          const int row = w.m0 + row_in_tile;
+          const int col0 = w.n0 + c32 * 32;
+          if (p.mul == nullptr || row >= p.m) return;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.mul) +
+                               2 * (w.batch * p.out_batch_stride + static_cast<long long>(row) * p.out_ld + col0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col0 + 8 * j < p.n) {
+              const uint4 g = *reinterpret_cast<const uint4*>(src + 16 * j);
+              const float2 g0 = unpack2(g.x, is_bf16), g1 = unpack2(g.y, is_bf16);
+              const float2 g2 = unpack2(g.z, is_bf16), g3 = unpack2(g.w, is_bf16);
+              v[8 * j + 0] *= g0.x;
+              v[8 * j + 1] *= g0.y;
+              v[8 * j + 2] *= g1.x;
+              v[8 * j + 3] *= g1.y;
+              v[8 * j + 4] *= g2.x;
+              v[8 * j + 5] *= g2.y;
+              v[8 * j + 6] *= g3.x;
+              v[8 * j + 7] *= g3.y;
+            }
+          }
+        }
+      };
+      // The same for one element of the transposed or narrow-slice forms (`index` as into `out`).
+      auto gate_elem = [&](float x, long long index) {
+        if constexpr (T::ACT) {
+          if (p.mul != nullptr) return x * load_elem(p.mul, w.batch * p.out_batch_stride + index, is_bf16);
+        }
+        return x;
+      };
+
       // Finish one chunk of up to 32 fp32 values of this thread's row (bias, round,
       // store).  `c32` indexes 32-column chunks of the output tile.
       auto finish_chunk = [&](float (&v)[32], int c32) {
@@ -691,7 +732,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < CHUNK_COLS; ++j) {
               const int col = w.n0 + c32 * 32 + j;
-              if (col < p.n) store_elem(base, col * p.out_ld + row, apply_act(v[j] + bias_v, act), is_bf16);
+              if (col < p.n) {
+                const long long at = static_cast<long long>(col) * p.out_ld + row;
+                store_elem(base, at, gate_elem(apply_act(v[j] + bias_v, act), at), is_bf16);
+              }
             }
           }
         } else {
@@ -710,6 +754,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < CHUNK_COLS; ++j) v[j] = apply_act(v[j], act);
           }
+          gate_chunk(v, c32);
           // Two 32-column chunks fill one 64-column (128-byte) store row.
           const int half = c32 & 1;
           if (half == 0) {
@@ -890,6 +935,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
                       for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
                     }
+                    gate_chunk(v, c32);
                     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) +
                                    2 * (w.batch * p.out_batch_stride + static_cast<long long>(row) * p.out_ld + col0);
 #pragma unroll
@@ -925,7 +971,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   if constexpr (T::EPI == EPI_BIAS) bias_v = load_elem(p.bias, row, is_bf16);
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
-                    if (col + j < p.n) store_elem(base, (col + j) * p.out_ld + row, apply_act(v4[j] + bias_v, act), is_bf16);
+                    if (col + j < p.n) {
+                      const long long at = static_cast<long long>(col + j) * p.out_ld + row;
+                      store_elem(base, at, gate_elem(apply_act(v4[j] + bias_v, act), at), is_bf16);
+                    }
                   }
                 } else {
                   if constexpr (T::EPI == EPI_BIAS) {
@@ -933,7 +982,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     for (int j = 0; j < 4; ++j) v4[j] += load_elem(p.bias, col + j, is_bf16);
                   }
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) v4[j] = apply_act(v4[j], act);
+                  for (int j = 0; j < 4; ++j) {
+                    v4[j] = gate_elem(apply_act(v4[j], act), static_cast<long long>(row) * p.out_ld + col + j);
+                  }
                   uint2 pk;
                   pk.x = pack2(v4[0], v4[1], is_bf16);
                   pk.y = pack2(v4[2], v4[3], is_bf16);

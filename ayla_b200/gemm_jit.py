@@ -195,9 +195,9 @@ class GemmLauncher:
     """
 
     def __init__(self, operation: str, dtype: str, batch: int, m: int, n: int, k: int,
-                 seed: GemmScheduleSeed, device: torch.device, activation: str = "none"):
+                 seed: GemmScheduleSeed, device: torch.device, activation: str = "none", gated: bool = False):
         assert seed.builder_config is not None
-        self.operation, self.dtype, self.activation = operation, dtype, activation
+        self.operation, self.dtype, self.activation, self.gated = operation, dtype, activation, gated
         self.batch, self.m, self.n, self.k = batch, m, n, k
         self.seed = seed
         self.device = device
@@ -214,7 +214,7 @@ class GemmLauncher:
         # Everything that does not change from call to call, converted for the C call once.
         import ctypes
 
-        self._entry = _lib.load().ayla_b200_gemm_act
+        self._entry = _lib.load().ayla_b200_gemm_act_mul
         self._head = (_lib.OP_CODES[operation], _lib.DTYPE_CODES[dtype], _lib.ACT_CODES[activation])
         self._tail = (batch, m, n, k, ctypes.byref(self.config), self._ws_ptr or None,
                       self.workspace.numel() if self.workspace is not None else 0, self._status_ptr)
@@ -222,13 +222,16 @@ class GemmLauncher:
         self._device_index = index
 
     def __call__(self, *tensors: torch.Tensor) -> None:
+        bias_ptr = mul_ptr = None
         if self._has_bias:
-            bias, a, bt, out = tensors
-            bias_ptr = bias.data_ptr()
+            bias_ptr = tensors[0].data_ptr()
+            tensors = tensors[1:]
+        if self.gated:
+            a, bt, mul, out = tensors
+            mul_ptr = mul.data_ptr()
         else:
             a, bt, out = tensors
-            bias_ptr = None
-        code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), out.data_ptr(), *self._tail,
+        code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), mul_ptr, out.data_ptr(), *self._tail,
                            torch.cuda.current_stream(self._device_index).cuda_stream)
         if code:
             _lib.check(code)
@@ -247,35 +250,39 @@ class GemmLauncher:
             )
 
 
-def _op_name(operation: str, dtype: str, activation: str = "none") -> str:
-    middle = "" if activation == "none" else f"_{activation}"
+def _op_name(operation: str, dtype: str, activation: str = "none", gated: bool = False) -> str:
+    middle = ("" if activation == "none" else f"_{activation}") + ("_mul" if gated else "")
     return f"jit_{operation}{middle}_{_SHORT_DTYPES[dtype]}"
 
 
-def _template(operation: str, dtype: str, activation: str = "none") -> OpTemplate:
+def _template(operation: str, dtype: str, activation: str = "none", gated: bool = False) -> OpTemplate:
     torch_dtype = _TORCH_DTYPES[dtype]
     rank = 3 if operation == "bmm" else 2
     tensor = TensorSpec(torch_dtype, (None,) * rank)
-    signature = (tensor, tensor, tensor)
+    signature = (tensor,) * (4 if gated else 3)  # a, bt, [mul,] out
     if operation == "addmm":
         signature = (TensorSpec(torch_dtype, (None,)), *signature)
-    return OpTemplate(_op_name(operation, dtype, activation), signature)
+    return OpTemplate(_op_name(operation, dtype, activation, gated), signature)
 
 
-def gemm_jit_compiler(operation: str, dtype: str, activation: str = "none") -> ShapeSpecializingJITCompiler:
+def gemm_jit_compiler(operation: str, dtype: str, activation: str = "none",
+                      gated: bool = False) -> ShapeSpecializingJITCompiler:
     """Per-shape dispatcher for one op: validates operands, picks the schedule once
     per ``(device, shapes)`` and launches (ayla/gemm_jit.py:339-393).  ``activation``
-    (one of ``ACTIVATIONS``) is fused into the epilogue."""
+    (one of ``ACTIVATIONS``) is fused into the epilogue; with ``gated`` the op takes one more
+    operand ``mul`` (shaped like ``out``, before it) and writes ``activation(...) * mul``."""
     if operation not in _OPERATIONS:
         raise ValueError(f"unsupported GEMM operation {operation}")
     if dtype not in _SHORT_DTYPES:
         raise ValueError(f"unsupported GEMM dtype {dtype}")
     if activation not in ACTIVATIONS:
         raise ValueError(f"unsupported GEMM activation {activation}")
-    template = _template(operation, dtype, activation)
+    template = _template(operation, dtype, activation, gated)
 
     def compile_specialization(bound: OpTemplate, device: torch.device) -> GemmLauncher:
-        *bias, a, bt, out = (spec.sizes for spec in bound.signature)
+        sizes = [spec.sizes for spec in bound.signature]
+        mul = sizes.pop(-2) if gated else None
+        *bias, a, bt, out = sizes
         *batch, m, k = a
         n = bt[-2]
         lead = tuple(batch)
@@ -288,10 +295,12 @@ def gemm_jit_compiler(operation: str, dtype: str, activation: str = "none") -> S
             raise ValueError(f"{bound.name}: out must be {(*lead, m, n)}, got {tuple(out)}")
         if bias and tuple(bias[0]) != (n,):
             raise ValueError(f"{bound.name}: bias must be ({n},), got {tuple(bias[0])}")
+        if mul is not None and tuple(mul) != tuple(out):
+            raise ValueError(f"{bound.name}: mul must have the shape of out {tuple(out)}, got {tuple(mul)}")
         schedule = select_gemm_schedule(operation, dtype, m, n, k, *batch)
         if schedule is None:
             raise ValueError(f"{bound.name}: no schedule for {operation} {lead}x{m}x{n}x{k}")
-        return GemmLauncher(operation, dtype, batch[0] if batch else 1, m, n, k, schedule, device, activation)
+        return GemmLauncher(operation, dtype, batch[0] if batch else 1, m, n, k, schedule, device, activation, gated)
 
     return ShapeSpecializingJITCompiler(template, compile_specialization)
 
@@ -323,6 +332,27 @@ def gemm_op_compiler(operation: str, dtype: str,
     size and the launchers' status words)."""
     gemm_op(operation, dtype, namespace)
     return _COMPILERS[(operation, dtype, namespace)]
+
+
+def gemm_act_mul_op(operation: str, activation: str, dtype: str,
+                    namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
+    """Torch op ``(bias?, a, bt, mul, out) -> ()`` writing ``out = activation([bias +] a @ bt^T) * mul``
+    with ``mul`` shaped like ``out``, named ``jit_{operation}[_{activation}]_mul_{f16|bf16}``: a gated
+    projection (``sigmoid(x @ Wg^T) * v``) in one kernel, the product taken in fp32 before the single
+    rounding.  The reference recognises this producer region in compiled graphs
+    (ayla/torch_compile.py:288-504) but has no kernel for it."""
+    return _gemm_act_mul_op(operation, activation, dtype, namespace)
+
+
+@cache
+def _gemm_act_mul_op(operation: str, activation: str, dtype: str, namespace: str) -> torch._ops.OpOverload:
+    from .torch_custom_call import make_torch_custom_call
+
+    compiler = gemm_jit_compiler(operation, dtype, activation, gated=True)
+    _COMPILERS[(f"{operation}_{activation}_mul", dtype, namespace)] = compiler
+    inputs = 4 if operation == "addmm" else 3
+    return make_torch_custom_call(compiler, [OperandKind.R] * inputs + [OperandKind.RW],
+                                  namespace=namespace)
 
 
 def gemm_act_op(operation: str, activation: str, dtype: str,

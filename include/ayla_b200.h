@@ -129,6 +129,18 @@ AYLA_B200_API int ayla_b200_gemm_act(int op, int dtype, int activation, const vo
                                      size_t workspace_bytes, uint32_t* status, void* stream);
 
 /*
+ * ayla_b200_gemm_act with a gate: out = act([bias +] a @ bt^T) * mul, where `mul` has the shape,
+ * type and layout of `out` (NULL = no gate) and enters in fp32 before the single rounding.  It
+ * serves gated projections such as sigmoid(x @ Wg^T) * v, the producer half of the
+ * `mm -> sigmoid -> mul -> mm` region the reference's Inductor pass recognises but has no kernel
+ * for (ayla/torch_compile.py:288-504).  `mul` must not alias `out`.
+ */
+AYLA_B200_API int ayla_b200_gemm_act_mul(int op, int dtype, int activation, const void* bias, const void* a,
+                                         const void* bt, const void* mul, void* out, int64_t batch, int64_t m,
+                                         int64_t n, int64_t k, const ayla_b200_config* cfg, void* workspace,
+                                         size_t workspace_bytes, uint32_t* status, void* stream);
+
+/*
  * Size of the scratch array built into the library for
  * ayla_b200_gemm_static_scratch: 8 MiB of device memory on every GPU that loads
  * the library, held until the process exits.

@@ -332,6 +332,59 @@ def test_fused_activation_epilogue(activation, device_state):
             assert_parity(out.cpu(), want, f"{activation} {operation} {batch}x{m}x{n}x{k} {cfg}")
 
 
+@pytest.mark.parametrize("activation", ["none", "sigmoid", "silu"])
+def test_gated_activation_epilogue(activation, device_state):
+    """act([bias +] a @ bt.T) * mul through the bulk-store, transposed, workspace split-K and cluster
+    split-K epilogues (ragged shapes: the gate is read only where `out` is written)."""
+    torch.manual_seed(3 + len(activation))
+    status, workspace = device_state
+    schedules = [dict(tile_n=256, cta_group=2), dict(tile_n=128, cta_group=1, split_k=2),
+                 dict(tile_n=128, cta_group=1, split_k=2, cluster_split=1),
+                 dict(tile_n=128, cta_group=1, split_k=4, cluster_split=1),
+                 dict(tile_n=64, cta_group=2, split_k=2, cluster_split=1),
+                 dict(tile_n=16, cta_group=1, swap_ab=1, group_m=1),
+                 dict(tile_n=32, cta_group=1, swap_ab=1, group_m=1, split_k=4, cluster_split=1),
+                 dict(tile_n=64, cta_group=1, swap_ab=1, group_m=1, split_k=3)]
+    for cfg in schedules:
+        small = bool(cfg.get("swap_ab"))
+        for operation, dtype, batch, m, n, k in (("mm", "bfloat16", 1, 24 if small else 300, 520, 1024),
+                                                 ("addmm", "float16", 1, 16 if small else 256, 264, 512),
+                                                 ("bmm", "bfloat16", 2, 8 if small else 200, 136, 512)):
+            config = _lib.Config.from_dict(cfg)
+            lead = (batch,) if operation == "bmm" else ()
+            a = torch.randn((*lead, m, k)).to(TD[dtype])
+            bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+            mul = torch.randn((*lead, m, n)).to(TD[dtype])
+            tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+            dev = [t.to(DEV) for t in tensors]
+            out = torch.full((*lead, m, n), float("nan"), dtype=TD[dtype], device=DEV)
+            status.zero_()
+            _lib.gemm_act_mul(operation, dtype, activation, dev[0].data_ptr() if operation == "addmm" else 0,
+                              dev[-2].data_ptr(), dev[-1].data_ptr(), mul.to(DEV).data_ptr(), out.data_ptr(),
+                              batch, m, n, k, config, workspace.data_ptr(), workspace.numel(), status.data_ptr(),
+                              torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            want = O.act_ref32(activation, O.gemm_ref32(operation, *tensors)) * mul.float()
+            assert_parity(out.cpu(), want, f"{activation}*mul {operation} {batch}x{m}x{n}x{k} {cfg}")
+
+
+def test_gemm_act_mul_op_matches_the_oracle():
+    from ayla_b200 import gemm_act_mul_op
+
+    torch.manual_seed(12)
+    a = torch.randn(192, 320).to(torch.bfloat16)
+    bt = (torch.randn(264, 320) * 320 ** -0.5).to(torch.bfloat16)
+    mul = torch.randn(192, 264).to(torch.bfloat16)
+    out = torch.empty(192, 264, dtype=torch.bfloat16, device=DEV)
+    op = gemm_act_mul_op("mm", "sigmoid", "bfloat16")
+    assert op is torch.ops.ayla.jit_mm_sigmoid_mul_bf16.default
+    assert op(a.to(DEV), bt.to(DEV), mul.to(DEV), out) is None
+    assert_parity(out.cpu(), torch.sigmoid(O.mm_ref32(a, bt)) * mul.float(), "jit_mm_sigmoid_mul_bf16")
+    with pytest.raises(ValueError, match="mul must have the shape of out"):
+        op(a.to(DEV), bt.to(DEV), mul[:100].contiguous().to(DEV), out)
+
+
 def test_gemm_act_op_matches_the_oracle():
     from ayla_b200.gemm_jit import gemm_act_op
 
