@@ -34,22 +34,22 @@ _DTYPE_NAMES = {torch.float16: "float16", torch.bfloat16: "bfloat16"}
 
 @cache
 def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE,
-               activation: str = "none") -> torch._ops.OpOverload:
-    """Functional form ``(bias?, a, bt) -> out`` of ``gemm_op`` / ``gemm_act_op`` (the result is
-    allocated by the op), the form a functional FX graph can hold.  Counterpart of the
-    reference's allocating ops (ayla/gemm_collection/dynamic_m.py:90-121)."""
-    compiler = gemm_jit_compiler(operation, dtype, activation)
+               activation: str = "none", gated: bool = False) -> torch._ops.OpOverload:
+    """Functional form ``(bias?, a, bt[, mul]) -> out`` of ``gemm_op`` / ``gemm_act_op`` /
+    ``gemm_act_mul_op`` (the result is allocated by the op), the form a functional FX graph can
+    hold.  Counterpart of the reference's allocating ops (ayla/gemm_collection/dynamic_m.py:90-121)."""
+    compiler = gemm_jit_compiler(operation, dtype, activation, gated)
 
     def infer(*inputs: torch.Tensor):
-        a, bt = inputs[-2], inputs[-1]
+        a, bt = (inputs[-3], inputs[-2]) if gated else (inputs[-2], inputs[-1])
         return [(*a.shape[:-1], bt.shape[-2])]
 
-    inputs = 3 if operation == "addmm" else 2
+    inputs = (3 if operation == "addmm" else 2) + (1 if gated else 0)
     return make_torch_custom_call(
         compiler,
         [OperandKind.R] * inputs + [OperandKind.RESULT],
         namespace=namespace,
-        name=f"{_op_name(operation, dtype, activation)}_fn",
+        name=f"{_op_name(operation, dtype, activation, gated)}_fn",
         infer_result_shapes=infer,
     )
 
@@ -336,6 +336,57 @@ def route_activations(graph: torch.fx.Graph) -> int:
     return rewritten
 
 
+def route_gated(graph: torch.fx.Graph) -> int:
+    """Rewrite ``act(gemm) * other`` (or ``gemm * other``) -- a claimed mm/addmm/bmm that only this
+    product reads, times a contiguous tensor of the result's shape and type -- into one call of the
+    gated op.  This is the producer half of the gated-attention output projection the reference's
+    pass matches without having a kernel for it (ayla/torch_compile.py:288-504)."""
+    rewritten = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten.mul.Tensor) or len(node.args) != 2:
+            continue
+        for lhs_arg, other in (node.args, node.args[::-1]):
+            if not isinstance(lhs_arg, torch.fx.Node) or not isinstance(other, torch.fx.Node):
+                continue
+            found = _activation_source(lhs_arg)
+            if found is not None:
+                activation, src, chain = found
+                fv, sv = _val(lhs_arg), _val(src)
+                if fv is None or sv is None or fv.dtype != sv.dtype:
+                    continue
+            else:
+                activation, src, chain = "none", lhs_arg, []
+            operands = _gemm_operands(src)
+            if operands is None or _gemm_operands(other) is not None:
+                continue  # two products: that is SwiGLU's pattern, or not ours at all
+            operation, lhs, rhs, bias = operands
+            claim = _claim(operation, lhs, rhs, bias)
+            ov, nv = _val(other), _val(node)
+            if claim is None or ov is None or nv is None:
+                continue
+            shape, stride = _static_ints(ov.shape), _static_ints(ov.stride())
+            if (ov.dtype != nv.dtype or _DTYPE_NAMES.get(ov.dtype) != claim[0] or shape is None
+                    or shape != _static_ints(nv.shape) or stride != _static_ints(nv.new_empty(shape).stride())):
+                continue  # broadcast, mixed types or a strided gate: leave it to Inductor
+            members = set(chain) | {node}
+            if not (_only_used_by(src, members) and all(_only_used_by(n, members) for n in chain)):
+                continue
+            with graph.inserting_before(node):
+                perm = [0, 2, 1] if operation == "bmm" else [1, 0]
+                bt = graph.call_function(aten.permute.default, (rhs, perm))
+                bt.meta["val"] = _val(rhs).permute(perm)
+                args = (lhs, bt, other) if bias is None else (bias, lhs, bt, other)
+                new = graph.call_function(gemm_fn_op(operation, claim[0], DEFAULT_NAMESPACE, activation, True), args)
+                new.meta.update({k: v for k, v in node.meta.items() if k != "original_aten"})
+            node.replace_all_uses_with(new)
+            graph.erase_node(node)
+            rewritten += 1
+            break
+    if rewritten:
+        graph.eliminate_dead_code()
+    return rewritten
+
+
 def route_swiglu_concat(graph: torch.fx.Graph) -> int:
     """Rewrite SwiGLU on a concatenated weight, ``g, u = (x @ w.T).chunk(2, -1); silu(g) * u``
     with ``w`` of shape ``[2 n, k]`` (the form real decoder blocks use,
@@ -441,6 +492,7 @@ class AylaRoutingPass(CustomGraphPass):
     def __call__(self, graph: torch.fx.Graph) -> None:
         route_swiglu(graph)  # first: it consumes two mm nodes route_gemms would claim
         route_swiglu_concat(graph)
+        route_gated(graph)
         route_activations(graph)
         route_gemms(graph)
         if self.previous is not None:
@@ -468,6 +520,8 @@ def install() -> None:
         for operation in ("mm", "addmm", "bmm"):
             for activation in ("relu", "sigmoid", "silu", "gelu"):
                 gemm_fn_op(operation, dtype, DEFAULT_NAMESPACE, activation)
+            for activation in ("none", "sigmoid", "silu"):
+                gemm_fn_op(operation, dtype, DEFAULT_NAMESPACE, activation, True)
     current = inductor_config.post_grad_custom_post_pass
     if _installed is not None and current is _installed:
         return

@@ -127,6 +127,27 @@ def test_activation_after_a_gemm_is_fused(activation):
     assert tc.route_activations(gm.graph) == 0
 
 
+def test_gated_product_is_fused():
+    import torch.nn.functional as F
+
+    specs = (((64, 32), BF16, "cuda"), ((48, 32), BF16, "cuda"), ((64, 48), BF16, "cuda"))
+    for name, fn in (("sigmoid_mul", lambda a, bt, v: torch.sigmoid(torch.mm(a, bt.t())) * v),
+                     ("silu_mul", lambda a, bt, v: v * F.silu(torch.mm(a, bt.t()))),
+                     ("mul", lambda a, bt, v: torch.mm(a, bt.t()) * v)):
+        gm = trace(fn, *specs)
+        assert tc.route_gated(gm.graph) == 1
+        gm.graph.lint()
+        assert getattr(torch.ops.ayla, f"jit_mm_{name}_bf16_fn").default in targets(gm)
+        assert not {aten.mm.default, aten.mul.Tensor, aten.sigmoid.default} & set(targets(gm))
+    # a broadcast gate, a gate of another type, or a product that is read elsewhere: left alone
+    gm = trace(lambda a, bt, v: torch.sigmoid(torch.mm(a, bt.t())) * v, specs[0], specs[1], ((48,), BF16, "cuda"))
+    assert tc.route_gated(gm.graph) == 0
+    gm = trace(lambda a, bt, v: torch.sigmoid(torch.mm(a, bt.t())) * v, specs[0], specs[1], ((64, 48), F32, "cuda"))
+    assert tc.route_gated(gm.graph) == 0
+    gm = trace(lambda a, bt, v: (lambda prod: (torch.sigmoid(prod) * v, prod))(torch.mm(a, bt.t())), *specs)
+    assert tc.route_gated(gm.graph) == 0
+
+
 def test_swiglu_on_a_concatenated_weight_is_fused():
     import torch.nn.functional as F
 
@@ -253,6 +274,27 @@ def test_torch_compile_fuses_activation_into_the_gemm(activation, ayla_installed
     torch.testing.assert_close(actual, expected, atol=0.05, rtol=0.02)
     assert any(f"jit_addmm_{activation}_bf16" in source for source in code)
     assert not any("triton" in source and "sigmoid" in source for source in code)
+
+
+@pytest.mark.gpu
+def test_torch_compile_fuses_a_gated_projection(ayla_installed):
+    """sigmoid(x @ Wg.T) * v followed by the output projection: the gate becomes one kernel."""
+    from torch._inductor.utils import run_and_get_code
+
+    x = torch.randn(200, 256, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(200, 264, device="cuda", dtype=torch.bfloat16)
+    wg = (torch.randn(264, 256, device="cuda") * 256 ** -0.5).bfloat16()
+    wo = (torch.randn(256, 264, device="cuda") * 264 ** -0.5).bfloat16()
+
+    def gated(x, v, wg, wo):
+        return torch.mm(torch.sigmoid(torch.mm(x, wg.T)) * v, wo.T)
+
+    with torch.no_grad(), inductor_config.patch(force_disable_caches=True):
+        actual, code = run_and_get_code(torch.compile(gated, fullgraph=True, dynamic=False), x, v, wg, wo)
+    expected = ((torch.sigmoid(x.float() @ wg.float().T) * v.float()).bfloat16().float() @ wo.float().T).bfloat16()
+    torch.testing.assert_close(actual, expected, atol=0.06, rtol=0.03)
+    assert any("jit_mm_sigmoid_mul_bf16" in source for source in code)
+    assert any("jit_mm_bf16" in source for source in code)
 
 
 @pytest.mark.gpu
