@@ -69,7 +69,7 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
             for s in (2, 4, 8):
                 if k_blocks >= 4 * s and w % (4 * s) == 0:
                     out.append(dict(base, split_k=s, cluster_split=1))
-    for tile_n in (64, 128, 256):
+    for tile_n in (64, 128, 192, 256):
         if tile_n > 64 and n < tile_n // 2:
             continue
         for cta_group in (1, 2):
@@ -77,16 +77,16 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
                 continue
             base = dict(tile_n=tile_n, cta_group=cta_group, group_m=8)
             out.append(dict(base))
-            if tile_n >= 128:
+            if tile_n % 128 == 0:
                 out.append(dict(base, split_tail=2))
             tiles = batch * -(-m // (128 * cta_group)) * -(-n // tile_n)
             if tiles * cta_group <= SM_COUNT:
                 for s in splits[:3]:
                     out.append(dict(base, split_k=s))
                 for s in (2, 4, 8):
-                    if s * cta_group <= 4 and k_blocks >= 4 * s and tiles * s * cta_group <= 2 * SM_COUNT:
+                    if tile_n != 192 and s * cta_group <= 4 and k_blocks >= 4 * s and tiles * s * cta_group <= 2 * SM_COUNT:
                         out.append(dict(base, split_k=s, cluster_split=1))
-                if cta_group == 1 and k_blocks >= 32 and tiles * 8 <= 2 * SM_COUNT:
+                if tile_n != 192 and cta_group == 1 and k_blocks >= 32 and tiles * 8 <= 2 * SM_COUNT:
                     out.append(dict(base, split_k=8, cluster_split=1))
     return out
 

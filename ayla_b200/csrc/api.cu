@@ -214,8 +214,9 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
       return fail(AYLA_B200_E_UNSUPPORTED,
                   "cluster_split needs split_k in {2, 4, 8} and a cluster (split_k * cta_group) of at most 8 CTAs");
     }
-    if (c.tile_n % (4 * c.split_k) != 0) {
-      return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split needs tile_n to be a multiple of 4 * split_k");
+    if (c.tile_n % (4 * c.split_k) != 0 || (c.tile_n & (c.tile_n - 1)) != 0) {
+      return fail(AYLA_B200_E_UNSUPPORTED,
+                  "cluster_split needs a power-of-two tile_n that is a multiple of 4 * split_k");
     }
   }
   if (c.l2_prefetch < 0 || c.l2_prefetch > 256) {
@@ -227,9 +228,9 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
   if (c.stream_k && (swiglu || c.split_k != 1 || c.split_tail != 0)) {
     return fail(AYLA_B200_E_UNSUPPORTED, "stream_k excludes split_k > 1, split_tail and the SwiGLU kernel");
   }
-  if (c.split_tail == 2 && (swiglu || c.swap_ab || c.split_k != 1 || c.tile_n < 128)) {
+  if (c.split_tail == 2 && (swiglu || c.swap_ab || c.split_k != 1 || c.tile_n % 128 != 0)) {
     return fail(AYLA_B200_E_UNSUPPORTED,
-                "split_tail = 2 (half-width last wave) needs tile_n >= 128, split_k = 1 and no swap_ab");
+                "split_tail = 2 (half-width last wave) needs tile_n of 128 or 256, split_k = 1 and no swap_ab");
   }
   if (c.l2_hint_a < 0 || c.l2_hint_a > 2 || c.l2_hint_b < 0 || c.l2_hint_b > 2) {
     return fail(AYLA_B200_E_UNSUPPORTED, "L2 hints must be 0, 1 or 2");
@@ -250,8 +251,8 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
     if (c.tile_n != 16 && c.tile_n != 32 && c.tile_n != 64 && c.tile_n != 128) {
       return fail(AYLA_B200_E_UNSUPPORTED, "swap_ab needs tile_n in {16,32,64,128}, got %d", c.tile_n);
     }
-  } else if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256) {
-    return fail(AYLA_B200_E_UNSUPPORTED, "tile_n must be 64, 128 or 256, got %d", c.tile_n);
+  } else if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 192 && c.tile_n != 256) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "tile_n must be 64, 128, 192 or 256, got %d", c.tile_n);
   }
   return AYLA_B200_OK;
 }

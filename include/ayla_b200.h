@@ -56,7 +56,7 @@ extern "C" {
  * at 128 per CTA (256 per CTA pair).
  */
 typedef struct ayla_b200_config {
-  int32_t tile_n;    /* accumulator columns per tile: 16,32,64,128,256 (16/32 only with swap_ab) */
+  int32_t tile_n;    /* accumulator columns per tile: 16,32,64,128,192,256 (16/32 only with swap_ab, 192 only without) */
   int32_t cta_group; /* 1, or 2 = two CTAs share one 256-row tile */
   int32_t swap_ab;   /* 1 = compute out^T = bt @ a^T (rows of bt fill the 128-row tile); small M */
   int32_t split_k;   /* >= 1; > 1 needs a workspace */

@@ -31,7 +31,7 @@ def test_version_and_variants():
     variants = _lib.kernel_variants()
     keys = {(v["tile_n"], v["cta_group"], v["epilogue"], v["transposed_out"]) for v in variants}
     assert len(keys) == len(variants)
-    for tile_n in (64, 128, 256):
+    for tile_n in (64, 128, 192, 256):
         for cta_group in (1, 2):
             for epilogue in (0, 1):
                 assert (tile_n, cta_group, epilogue, 0) in keys

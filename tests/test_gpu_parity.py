@@ -136,7 +136,7 @@ def test_capture_time_cache_miss_is_an_error():
 
 # --------------------------------------------------- every kernel variant, ragged
 
-ROW_MAJOR = [(tile_n, cta_group) for tile_n in (64, 128, 256) for cta_group in (1, 2)]
+ROW_MAJOR = [(tile_n, cta_group) for tile_n in (64, 128, 192, 256) for cta_group in (1, 2)]
 SHAPES = [
     ("mm", 1, 128, 256, 64), ("mm", 1, 96, 128, 128), ("mm", 1, 333, 520, 200), ("mm", 1, 1, 8, 8),
     ("addmm", 1, 300, 264, 192), ("bmm", 3, 200, 136, 128), ("mm", 1, 1024, 768, 520),
