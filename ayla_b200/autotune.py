@@ -42,7 +42,8 @@ HEADLINE_SHAPES = [
     ("mm", "bfloat16", 1, 4096, 4096, 32768),
 ]
 # Projections of an 8B-class decoder that the sweep does not cover (fused QKV, concatenated gate/up).
-DECODER_SHAPES = [("mm", "bfloat16", 1, m, n, 4096) for n in (6144, 28672) for m in (8, 64, 512, 4096)]
+DECODER_SHAPES = ([("mm", "bfloat16", 1, m, 6144, 4096) for m in (8, 64, 256, 512, 1024, 2048, 4096)]
+                  + [("mm", "bfloat16", 1, m, 28672, 4096) for m in (8, 64, 512, 4096)])
 # Larger models: hidden 8192, FFN 28672 (70B-class layer shapes), decode and prefill row counts.
 LARGE_SHAPES = [("mm", "bfloat16", 1, m, n, k) for (n, k) in ((8192, 8192), (10240, 8192), (28672, 8192), (8192, 28672))
                 for m in (8, 64, 512, 4096)]
