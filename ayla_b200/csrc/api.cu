@@ -513,6 +513,9 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
       }
     }
   }
+  // bt is streamed (evict-first) only while every row tile that needs a column tile's slab runs
+  // in the same raster group; with more row tiles than that it is read again later and is kept.
+  if (ceil_div(m, 128 * c->cta_group) > c->group_m) c->l2_hint_b = 2;
 }
 
 int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, int is_bf16,
