@@ -54,7 +54,7 @@ FLOPS = 2.0 * M * N * K
 ALGO_BYTES = 2.0 * (M * K + N * K + M * N)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
 # summarised in profiles/ (None until measured).
-NCU_TRAFFIC_BYTES = 106.3e6
+NCU_TRAFFIC_BYTES = 100.7e6
 
 
 def read_peaks() -> dict:
