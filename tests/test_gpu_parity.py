@@ -608,3 +608,38 @@ def test_launcher_check_status_raises_on_timeout():
     compiler(a, a, out)
     launcher.check_status()
     torch.testing.assert_close(out, a @ a.T, atol=0.125, rtol=0.02)
+
+
+def test_random_shapes_through_the_public_ops():
+    """Schedule selection on shapes nobody measured: transferred table entries (trimmed tiles, 192-wide
+    tiles, cluster k-splits, eviction hints) and the default heuristic must all stay correct on ragged
+    extents.  Checked against the GPU's own fp32-accumulating matmul with the reference's test tolerances
+    (tests/test_gemm_jit.py:59-63 of the reference)."""
+    import random
+
+    rng = random.Random(1234)
+    torch.manual_seed(1234)
+    picks_m = [1, 3, 8, 17, 33, 64, 100, 128, 200, 256, 384, 512, 777, 1024, 1536, 2048, 3000]
+    picks_n = [8, 64, 136, 512, 1000, 2048, 4096, 6144, 7168, 8192, 11008, 14336]
+    picks_k = [8, 72, 128, 520, 1024, 2048, 4096, 5120, 8192, 14336]
+    for trial in range(120):
+        operation = rng.choice(["mm", "mm", "addmm", "bmm"])
+        m, n, k = rng.choice(picks_m), rng.choice(picks_n), rng.choice(picks_k)
+        batch = rng.choice([2, 3, 5]) if operation == "bmm" else 1
+        if batch * (m * k + n * k + m * n) > 160e6:
+            k = min(k, 1024)
+        dtype = rng.choice(["bfloat16", "float16"])
+        td = TD[dtype]
+        lead = (batch,) if operation == "bmm" else ()
+        a = torch.randn((*lead, m, k), device=DEV).to(td)
+        bt = (torch.randn((*lead, n, k), device=DEV) * k ** -0.5).to(td)
+        out = torch.full((*lead, m, n), float("nan"), device=DEV, dtype=td)
+        if operation == "addmm":
+            bias = torch.randn(n, device=DEV).to(td)
+            gemm_op(operation, dtype)(bias, a, bt, out)
+            want = torch.addmm(bias.float(), a.float(), bt.float().T)
+        else:
+            gemm_op(operation, dtype)(a, bt, out)
+            want = a.float() @ bt.float().transpose(-1, -2)
+        torch.testing.assert_close(out.float(), want, atol=0.125, rtol=0.02,
+                                   msg=lambda msg: f"{operation} {dtype} {batch}x{m}x{n}x{k}: {msg}")
