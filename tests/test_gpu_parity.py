@@ -643,3 +643,52 @@ def test_random_shapes_through_the_public_ops():
             want = a.float() @ bt.float().transpose(-1, -2)
         torch.testing.assert_close(out.float(), want, atol=0.125, rtol=0.02,
                                    msg=lambda msg: f"{operation} {dtype} {batch}x{m}x{n}x{k}: {msg}")
+
+
+def test_random_shapes_through_the_fused_ops():
+    """SwiGLU, activation and gated epilogues on ragged shapes nobody measured, against fp32 math on
+    the GPU rounded once (same tolerances as the plain ops)."""
+    import random
+
+    from ayla_b200 import ACTIVATIONS, gemm_act_mul_op, gemm_act_op
+
+    rng = random.Random(4321)
+    torch.manual_seed(4321)
+    acts = {"relu": torch.relu, "sigmoid": torch.sigmoid, "silu": torch.nn.functional.silu,
+            "gelu": torch.nn.functional.gelu,
+            "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}
+    assert set(acts) == set(ACTIVATIONS) - {"none"}
+    for trial in range(60):
+        m = rng.choice([1, 8, 24, 64, 130, 256, 512, 1000, 2048])
+        n = rng.choice([8, 72, 512, 1000, 4096, 6144, 14336])
+        k = rng.choice([8, 136, 1024, 4096, 5120])
+        dtype = rng.choice(["bfloat16", "float16"])
+        td = TD[dtype]
+        a = torch.randn(m, k, device=DEV).to(td)
+        w0 = (torch.randn(n, k, device=DEV) * k ** -0.5).to(td)
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=td)
+        kind = rng.choice(["swiglu", "act", "gated"])
+        if kind == "swiglu":
+            w1 = (torch.randn(n, k, device=DEV) * k ** -0.5).to(td)
+            swiglu_op(dtype)(a, w0, w1, out)
+            want = torch.nn.functional.silu(a.float() @ w0.float().T) * (a.float() @ w1.float().T)
+            label = "swiglu"
+        else:
+            act = rng.choice(sorted(acts))
+            with_bias = rng.random() < 0.5
+            bias = torch.randn(n, device=DEV).to(td)
+            want = a.float() @ w0.float().T
+            if with_bias:
+                want = want + bias.float()
+            want = acts[act](want)
+            operation = "addmm" if with_bias else "mm"
+            lead = (bias,) if with_bias else ()
+            if kind == "act":
+                gemm_act_op(operation, act, dtype)(*lead, a, w0, out)
+            else:
+                mul = torch.randn(m, n, device=DEV).to(td)
+                gemm_act_mul_op(operation, act, dtype)(*lead, a, w0, mul, out)
+                want = want * mul.float()
+            label = f"{kind} {operation} {act}"
+        torch.testing.assert_close(out.float(), want, atol=0.125, rtol=0.02,
+                                   msg=lambda msg: f"{label} {dtype} {m}x{n}x{k}: {msg}")
