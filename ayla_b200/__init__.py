@@ -18,6 +18,7 @@ from .gemm_jit import (
     ACTIVATIONS,
     GemmScheduleSeed,
     gemm_act_mul_op,
+    gemm_act_rowmul_op,
     gemm_act_op,
     gemm_jit_compiler,
     gemm_op,
@@ -35,6 +36,7 @@ __all__ = [
     "OperandKind",
     "TensorSpec",
     "gemm_act_mul_op",
+    "gemm_act_rowmul_op",
     "gemm_act_op",
     "gemm_jit_compiler",
     "gemm_op",

@@ -24,6 +24,7 @@ EXPORTS = (
     "ayla_b200_gemm",
     "ayla_b200_gemm_act",
     "ayla_b200_gemm_act_mul",
+    "ayla_b200_gemm_act_rowmul",
     "ayla_b200_gemm_static_scratch",
     "ayla_b200_swiglu",
     "ayla_b200_default_config",
@@ -118,6 +119,8 @@ def load() -> ctypes.CDLL:
         lib.ayla_b200_gemm_act.restype = i32
         lib.ayla_b200_gemm_act_mul.argtypes = [i32, i32, i32, vp, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, sz, vp, vp]
         lib.ayla_b200_gemm_act_mul.restype = i32
+        lib.ayla_b200_gemm_act_rowmul.argtypes = lib.ayla_b200_gemm_act_mul.argtypes
+        lib.ayla_b200_gemm_act_rowmul.restype = i32
         lib.ayla_b200_gemm_static_scratch.argtypes = [i32, i32, vp, vp, vp, vp, i64, i64, i64, i64, cfgp, vp, vp]
         lib.ayla_b200_gemm_static_scratch.restype = i32
         lib.ayla_b200_swiglu.argtypes = [i32, vp, vp, vp, vp, i64, i64, i64, cfgp, vp, vp]
@@ -240,6 +243,17 @@ def gemm_act_mul(op: str, dtype: str, activation: str, bias_ptr: int, a_ptr: int
     the one rounding."""
     check(load().ayla_b200_gemm_act_mul(
         OP_CODES[op], DTYPE_CODES[dtype], ACT_CODES[activation], bias_ptr or None, a_ptr, bt_ptr, mul_ptr or None,
+        out_ptr, batch, m, n, k, ctypes.byref(cfg) if cfg is not None else None, workspace_ptr or None,
+        workspace_size, status_ptr or None, stream or None))
+
+
+def gemm_act_rowmul(op: str, dtype: str, activation: str, bias_ptr: int, a_ptr: int, bt_ptr: int, row_mul_ptr: int,
+                    out_ptr: int, batch: int, m: int, n: int, k: int, cfg: Config | None, workspace_ptr: int,
+                    workspace_size: int, status_ptr: int, stream: int) -> None:
+    """``gemm_act`` followed by a product with one factor per output row (``batch * m`` elements of the
+    operands' type), still before the one rounding."""
+    check(load().ayla_b200_gemm_act_rowmul(
+        OP_CODES[op], DTYPE_CODES[dtype], ACT_CODES[activation], bias_ptr or None, a_ptr, bt_ptr, row_mul_ptr or None,
         out_ptr, batch, m, n, k, ctypes.byref(cfg) if cfg is not None else None, workspace_ptr or None,
         workspace_size, status_ptr or None, stream or None))
 

@@ -521,7 +521,7 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
 int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, int is_bf16,
                 const void* bias, const void* b2_operand, void* out, int64_t out_rows,
                 int64_t out_cols, void* workspace, size_t workspace_bytes, uint32_t* status,
-                cudaStream_t stream, int activation = 0, const void* mul = nullptr) {
+                cudaStream_t stream, int activation = 0, const void* mul = nullptr, int mul_per_row = 0) {
   const KernelEntry& e = *plan.kernel;
   LaunchArgs la;
   memset(&la, 0, sizeof(la));
@@ -593,6 +593,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.tile_rows = plan.tile_rows;
   p.act = activation;
   p.mul = mul;
+  p.mul_per_row = mul_per_row;
   // One stage receives this CTA's rows of the row operand and its share of the column
   // operand; the leader of a pair counts both CTAs' bytes.
   p.stage_tx = static_cast<uint32_t>((a_box_rows + b_stage_rows) * 128 * e.cta_group);
@@ -775,6 +776,11 @@ int ayla_b200_gemm_act(int op, int dtype, int activation, const void* bias, cons
                                 workspace_bytes, status, stream);
 }
 
+static int gemm_fused(int op, int dtype, int activation, const void* bias, const void* a, const void* bt,
+                      const void* mul, int mul_per_row, void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
+                      const ayla_b200_config* cfg, void* workspace, size_t workspace_bytes, uint32_t* status,
+                      void* stream);
+
 int ayla_b200_gemm_act_mul(int op, int dtype, int activation, const void* bias, const void* a, const void* bt,
                            const void* mul, void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
                            const ayla_b200_config* cfg, void* workspace, size_t workspace_bytes,
@@ -782,6 +788,25 @@ int ayla_b200_gemm_act_mul(int op, int dtype, int activation, const void* bias, 
   if (mul != nullptr && !aligned16(mul)) {
     return fail(AYLA_B200_E_UNSUPPORTED, "mul must be 16-byte aligned");
   }
+  return gemm_fused(op, dtype, activation, bias, a, bt, mul, 0, out, batch, m, n, k, cfg, workspace,
+                    workspace_bytes, status, stream);
+}
+
+int ayla_b200_gemm_act_rowmul(int op, int dtype, int activation, const void* bias, const void* a, const void* bt,
+                              const void* row_mul, void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
+                              const ayla_b200_config* cfg, void* workspace, size_t workspace_bytes,
+                              uint32_t* status, void* stream) {
+  if (row_mul == nullptr || (reinterpret_cast<uintptr_t>(row_mul) & 1) != 0) {
+    return fail(AYLA_B200_E_INVALID, "row_mul must be a non-null, 2-byte aligned pointer");
+  }
+  return gemm_fused(op, dtype, activation, bias, a, bt, row_mul, 1, out, batch, m, n, k, cfg, workspace,
+                    workspace_bytes, status, stream);
+}
+
+static int gemm_fused(int op, int dtype, int activation, const void* bias, const void* a, const void* bt,
+                      const void* mul, int mul_per_row, void* out, int64_t batch, int64_t m, int64_t n, int64_t k,
+                      const ayla_b200_config* cfg, void* workspace, size_t workspace_bytes, uint32_t* status,
+                      void* stream) {
   int rc = check_shape(op, dtype, batch, m, n, k);
   if (rc) return rc;
   if (activation < AYLA_B200_ACT_NONE || activation > AYLA_B200_ACT_GELU_TANH) {
@@ -829,7 +854,7 @@ int ayla_b200_gemm_act_mul(int op, int dtype, int activation, const void* bias, 
   rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan, (activation != 0 || mul != nullptr) ? 1 : 0);
   if (rc) return rc;
   return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, workspace,
-                     workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream), activation, mul);
+                     workspace_bytes, status, reinterpret_cast<cudaStream_t>(stream), activation, mul, mul_per_row);
 }
 
 int ayla_b200_gemm_static_scratch(int op, int dtype, const void* bias, const void* a, const void* bt,

@@ -78,6 +78,7 @@ struct KernelParams {
   int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
   int l2_prefetch;    // k-blocks the producer prefetches into L2 ahead of its shared-memory loads
   const void* mul;    // optional gate, same shape and layout as `out`: out = act(...) * mul (activation variants)
+  int mul_per_row;    // non-zero: `mul` holds one element per output row instead ([batch][rows])
   int act;            // activation applied to the fp32 result (after the bias) before rounding: ACT_*
   int tile_rows;      // swapped form: rows of the row operand per tile (8..128); 128 otherwise
   uint32_t stage_tx;  // bytes one ring stage receives (both CTAs of a pair together)
@@ -689,6 +690,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const int row = w.m0 + row_in_tile;
           const int col0 = w.n0 + c32 * 32;
           if (p.mul == nullptr || row >= p.m) return;
+          if (p.mul_per_row) {
+            const float g = load_elem(p.mul, w.batch * static_cast<long long>(p.m) + row, is_bf16);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= g;
+            return;
+          }
           const uint8_t* src = reinterpret_cast<const uint8_t*>(p.mul) +
                                2 * (w.batch * p.out_batch_stride + static_cast<long long>(row) * p.out_ld + col0);
 #pragma unroll
@@ -709,10 +716,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           }
         }
       };
-      // The same for one element of the transposed or narrow-slice forms (`index` as into `out`).
-      auto gate_elem = [&](float x, long long index) {
+      // The same for one element of the transposed or narrow-slice forms (`index` as into `out`,
+      // `out_row` the element's row of the output matrix).
+      auto gate_elem = [&](float x, long long index, int out_row) {
         if constexpr (T::ACT) {
-          if (p.mul != nullptr) return x * load_elem(p.mul, w.batch * p.out_batch_stride + index, is_bf16);
+          if (p.mul != nullptr) {
+            const long long at = p.mul_per_row
+                                     ? w.batch * static_cast<long long>(T::TRANS_OUT ? p.n : p.m) + out_row
+                                     : w.batch * p.out_batch_stride + index;
+            return x * load_elem(p.mul, at, is_bf16);
+          }
         }
         return x;
       };
@@ -734,7 +747,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               const int col = w.n0 + c32 * 32 + j;
               if (col < p.n) {
                 const long long at = static_cast<long long>(col) * p.out_ld + row;
-                store_elem(base, at, gate_elem(apply_act(v[j] + bias_v, act), at), is_bf16);
+                store_elem(base, at, gate_elem(apply_act(v[j] + bias_v, act), at, col), is_bf16);
               }
             }
           }
@@ -973,7 +986,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   for (int j = 0; j < 4; ++j) {
                     if (col + j < p.n) {
                       const long long at = static_cast<long long>(col + j) * p.out_ld + row;
-                      store_elem(base, at, gate_elem(apply_act(v4[j] + bias_v, act), at), is_bf16);
+                      store_elem(base, at, gate_elem(apply_act(v4[j] + bias_v, act), at, col + j), is_bf16);
                     }
                   }
                 } else {
@@ -983,7 +996,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   }
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
-                    v4[j] = gate_elem(apply_act(v4[j], act), static_cast<long long>(row) * p.out_ld + col + j);
+                    v4[j] = gate_elem(apply_act(v4[j], act), static_cast<long long>(row) * p.out_ld + col + j, row);
                   }
                   uint2 pk;
                   pk.x = pack2(v4[0], v4[1], is_bf16);

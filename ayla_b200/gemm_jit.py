@@ -195,7 +195,8 @@ class GemmLauncher:
     """
 
     def __init__(self, operation: str, dtype: str, batch: int, m: int, n: int, k: int,
-                 seed: GemmScheduleSeed, device: torch.device, activation: str = "none", gated: bool = False):
+                 seed: GemmScheduleSeed, device: torch.device, activation: str = "none",
+                 gated: bool | str = False):
         assert seed.builder_config is not None
         self.operation, self.dtype, self.activation, self.gated = operation, dtype, activation, gated
         self.batch, self.m, self.n, self.k = batch, m, n, k
@@ -214,7 +215,8 @@ class GemmLauncher:
         # Everything that does not change from call to call, converted for the C call once.
         import ctypes
 
-        self._entry = _lib.load().ayla_b200_gemm_act_mul
+        lib = _lib.load()
+        self._entry = lib.ayla_b200_gemm_act_rowmul if gated == "row" else lib.ayla_b200_gemm_act_mul
         self._head = (_lib.OP_CODES[operation], _lib.DTYPE_CODES[dtype], _lib.ACT_CODES[activation])
         self._tail = (batch, m, n, k, ctypes.byref(self.config), self._ws_ptr or None,
                       self.workspace.numel() if self.workspace is not None else 0, self._status_ptr)
@@ -250,12 +252,12 @@ class GemmLauncher:
             )
 
 
-def _op_name(operation: str, dtype: str, activation: str = "none", gated: bool = False) -> str:
-    middle = ("" if activation == "none" else f"_{activation}") + ("_mul" if gated else "")
+def _op_name(operation: str, dtype: str, activation: str = "none", gated: bool | str = False) -> str:
+    middle = ("" if activation == "none" else f"_{activation}") + {False: "", True: "_mul", "row": "_rowmul"}[gated]
     return f"jit_{operation}{middle}_{_SHORT_DTYPES[dtype]}"
 
 
-def _template(operation: str, dtype: str, activation: str = "none", gated: bool = False) -> OpTemplate:
+def _template(operation: str, dtype: str, activation: str = "none", gated: bool | str = False) -> OpTemplate:
     torch_dtype = _TORCH_DTYPES[dtype]
     rank = 3 if operation == "bmm" else 2
     tensor = TensorSpec(torch_dtype, (None,) * rank)
@@ -266,11 +268,14 @@ def _template(operation: str, dtype: str, activation: str = "none", gated: bool 
 
 
 def gemm_jit_compiler(operation: str, dtype: str, activation: str = "none",
-                      gated: bool = False) -> ShapeSpecializingJITCompiler:
+                      gated: bool | str = False) -> ShapeSpecializingJITCompiler:
     """Per-shape dispatcher for one op: validates operands, picks the schedule once
     per ``(device, shapes)`` and launches (ayla/gemm_jit.py:339-393).  ``activation``
     (one of ``ACTIVATIONS``) is fused into the epilogue; with ``gated`` the op takes one more
-    operand ``mul`` (shaped like ``out``, before it) and writes ``activation(...) * mul``."""
+    operand ``mul`` (shaped like ``out``, before it) and writes ``activation(...) * mul``; with
+    ``gated="row"`` that operand is one factor per output row, shaped ``(..., m, 1)``."""
+    if gated not in (False, True, "row"):
+        raise ValueError(f"unsupported gate {gated!r}")
     if operation not in _OPERATIONS:
         raise ValueError(f"unsupported GEMM operation {operation}")
     if dtype not in _SHORT_DTYPES:
@@ -295,7 +300,9 @@ def gemm_jit_compiler(operation: str, dtype: str, activation: str = "none",
             raise ValueError(f"{bound.name}: out must be {(*lead, m, n)}, got {tuple(out)}")
         if bias and tuple(bias[0]) != (n,):
             raise ValueError(f"{bound.name}: bias must be ({n},), got {tuple(bias[0])}")
-        if mul is not None and tuple(mul) != tuple(out):
+        if gated == "row" and tuple(mul) != (*lead, m, 1):
+            raise ValueError(f"{bound.name}: the row factors must be {(*lead, m, 1)}, got {tuple(mul)}")
+        if gated is True and tuple(mul) != tuple(out):
             raise ValueError(f"{bound.name}: mul must have the shape of out {tuple(out)}, got {tuple(mul)}")
         schedule = select_gemm_schedule(operation, dtype, m, n, k, *batch)
         if schedule is None:
@@ -353,6 +360,29 @@ def _gemm_act_mul_op(operation: str, activation: str, dtype: str, namespace: str
     inputs = 4 if operation == "addmm" else 3
     return make_torch_custom_call(compiler, [OperandKind.R] * inputs + [OperandKind.RW],
                                   namespace=namespace)
+
+
+def gemm_act_rowmul_op(operation: str, activation: str, dtype: str,
+                       namespace: str = DEFAULT_NAMESPACE) -> torch._ops.OpOverload:
+    """Torch op ``(bias?, a, bt, row_mul, out) -> ()`` writing
+    ``out = activation([bias +] a @ bt^T) * row_mul`` with ``row_mul`` shaped ``(..., m, 1)`` (one factor
+    per output row, as a ``keepdim`` reduction over the rows of ``a`` leaves it), named
+    ``jit_{operation}[_{activation}]_rowmul_{f16|bf16}``.  With no activation and no bias it is a GEMM
+    whose left operand carries a per-row scale: an RMSNorm followed by a projection becomes one row
+    reduction and this op once the norm's weight vector is folded into ``bt``, because
+    ``(x * r[:, None] * g) @ W.T == r[:, None] * (x @ (W * g).T)``.  The reference lists epilogue
+    fusion as an aim (README.md:6-7) and has no kernel of this form."""
+    return _gemm_act_rowmul_op(operation, activation, dtype, namespace)
+
+
+@cache
+def _gemm_act_rowmul_op(operation: str, activation: str, dtype: str, namespace: str) -> torch._ops.OpOverload:
+    from .torch_custom_call import make_torch_custom_call
+
+    compiler = gemm_jit_compiler(operation, dtype, activation, gated="row")
+    _COMPILERS[(f"{operation}+{activation}+rowmul", dtype, namespace)] = compiler
+    inputs = 4 if operation == "addmm" else 3
+    return make_torch_custom_call(compiler, [OperandKind.R] * inputs + [OperandKind.RW], namespace=namespace)
 
 
 def gemm_act_op(operation: str, activation: str, dtype: str,

@@ -141,6 +141,20 @@ AYLA_B200_API int ayla_b200_gemm_act_mul(int op, int dtype, int activation, cons
                                          size_t workspace_bytes, uint32_t* status, void* stream);
 
 /*
+ * ayla_b200_gemm_act with one factor per output row: out[b][i][j] = act([bias +] a @ bt^T)[b][i][j]
+ * * row_mul[b][i], where `row_mul` holds batch * m elements of the operands' type, contiguous,
+ * and enters in fp32 before the single rounding.  With act = NONE and no bias this is a GEMM whose
+ * left operand carries a per-row scale, e.g. the 1/rms factor of an RMSNorm whose weight vector has
+ * been folded into `bt`: rmsnorm(x) @ W^T = rsqrt(mean(x^2) + eps)[i] * (x @ (W * g)^T).  The
+ * reference lists epilogue fusion as an aim (README.md:6-7) and has no kernel of this form.
+ */
+AYLA_B200_API int ayla_b200_gemm_act_rowmul(int op, int dtype, int activation, const void* bias, const void* a,
+                                            const void* bt, const void* row_mul, void* out, int64_t batch,
+                                            int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg,
+                                            void* workspace, size_t workspace_bytes, uint32_t* status,
+                                            void* stream);
+
+/*
  * Size of the scratch array built into the library for
  * ayla_b200_gemm_static_scratch: 8 MiB of device memory on every GPU that loads
  * the library, held until the process exits.

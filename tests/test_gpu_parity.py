@@ -369,6 +369,71 @@ def test_gated_activation_epilogue(activation, device_state):
             assert_parity(out.cpu(), want, f"{activation}*mul {operation} {batch}x{m}x{n}x{k} {cfg}")
 
 
+def test_row_factor_epilogue(device_state):
+    """act([bias +] a @ bt.T) * row_mul[:, None] through the bulk-store, transposed, workspace split-K
+    and cluster split-K epilogues."""
+    torch.manual_seed(77)
+    status, workspace = device_state
+    schedules = [dict(tile_n=256, cta_group=2), dict(tile_n=192, cta_group=1), dict(tile_n=128, cta_group=1, split_k=2),
+                 dict(tile_n=128, cta_group=1, split_k=2, cluster_split=1),
+                 dict(tile_n=128, cta_group=1, split_k=4, cluster_split=1),
+                 dict(tile_n=64, cta_group=2, split_k=2, cluster_split=1),
+                 dict(tile_n=16, cta_group=1, swap_ab=1, group_m=1),
+                 dict(tile_n=32, cta_group=1, swap_ab=1, group_m=1, split_k=4, cluster_split=1),
+                 dict(tile_n=128, cta_group=1, swap_ab=1, group_m=1, split_k=2, cluster_split=1),
+                 dict(tile_n=64, cta_group=1, swap_ab=1, group_m=1, split_k=3)]
+    for cfg in schedules:
+        small = bool(cfg.get("swap_ab"))
+        for operation, dtype, activation, batch, m, n, k in (
+                ("mm", "bfloat16", "none", 1, 24 if small else 300, 520, 1024),
+                ("addmm", "float16", "relu", 1, 16 if small else 256, 264, 512),
+                ("bmm", "bfloat16", "silu", 3, 8 if small else 200, 136, 512)):
+            config = _lib.Config.from_dict(cfg)
+            lead = (batch,) if operation == "bmm" else ()
+            a = torch.randn((*lead, m, k)).to(TD[dtype])
+            bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+            row_mul = (torch.rand((*lead, m, 1)) + 0.5).to(TD[dtype])
+            tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+            dev = [t.to(DEV) for t in tensors]
+            out = torch.full((*lead, m, n), float("nan"), dtype=TD[dtype], device=DEV)
+            status.zero_()
+            _lib.gemm_act_rowmul(operation, dtype, activation, dev[0].data_ptr() if operation == "addmm" else 0,
+                                 dev[-2].data_ptr(), dev[-1].data_ptr(), row_mul.to(DEV).data_ptr(), out.data_ptr(),
+                                 batch, m, n, k, config, workspace.data_ptr(), workspace.numel(), status.data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            want = O.act_ref32(activation, O.gemm_ref32(operation, *tensors)) * row_mul.float()
+            assert_parity(out.cpu(), want, f"{activation}*row {operation} {batch}x{m}x{n}x{k} {cfg}")
+
+
+def test_rms_norm_linear_matches_the_unfused_form():
+    """One row reduction + one GEMM against normalise-then-project in fp32 on the CPU, on a decode and
+    a prefill token count, through whichever schedules selection gives them."""
+    from ayla_b200 import gemm_act_rowmul_op
+    from ayla_b200.rmsnorm_linear import fold_norm_weight, rms_norm_linear
+
+    torch.manual_seed(5)
+    assert gemm_act_rowmul_op("mm", "none", "bfloat16") is torch.ops.ayla.jit_mm_rowmul_bf16.default
+    hidden, features = 1024, 1536
+    g = (1.0 + 0.1 * torch.randn(hidden)).to(torch.bfloat16)
+    w = (torch.randn(features, hidden) * hidden ** -0.5).to(torch.bfloat16)
+    folded = fold_norm_weight(w.to(DEV), g.to(DEV))
+    for tokens in (8, 300):
+        x = (torch.randn(tokens, hidden) * 3.0).to(torch.bfloat16)
+        got = rms_norm_linear(x.to(DEV), folded, eps=1e-5)
+        x32 = x.float()
+        normed = x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()
+        want = normed @ w.float().T
+        rel = float((got.cpu().float() - want).norm() / want.norm())
+        # Three roundings separate the two forms (folded weight, row factor, output): each at most 2^-9.
+        assert rel < 6e-3, (tokens, rel)
+    with pytest.raises(ValueError, match="row factors must be"):
+        gemm_act_rowmul_op("mm", "none", "bfloat16")(x.to(DEV), folded, torch.ones(300, device=DEV, dtype=torch.bfloat16)
+                                                     .view(1, 300), torch.empty(300, features, device=DEV,
+                                                                                dtype=torch.bfloat16))
+
+
 def test_gemm_act_mul_op_matches_the_oracle():
     from ayla_b200 import gemm_act_mul_op
 
