@@ -364,6 +364,38 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   }
 }
 
+// The same over the first COUNT values of a thread's chunk, with the choice of activation taken
+// once outside the loop: each activation gets its own short unrolled loop, so a launch executes
+// one contiguous piece of code instead of stepping through a switch per element.
+template <int COUNT, int N>
+__device__ __forceinline__ void apply_act_chunk(float (&v)[N], int act) {
+  static_assert(COUNT <= N, "chunk larger than its array");
+  switch (act) {
+    case ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < COUNT; ++j) v[j] = apply_act(v[j], ACT_RELU);
+      break;
+    case ACT_SIGMOID:
+#pragma unroll
+      for (int j = 0; j < COUNT; ++j) v[j] = apply_act(v[j], ACT_SIGMOID);
+      break;
+    case ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < COUNT; ++j) v[j] = apply_act(v[j], ACT_SILU);
+      break;
+    case ACT_GELU:
+#pragma unroll
+      for (int j = 0; j < COUNT; ++j) v[j] = apply_act(v[j], ACT_GELU);
+      break;
+    case ACT_GELU_TANH:
+#pragma unroll
+      for (int j = 0; j < COUNT; ++j) v[j] = apply_act(v[j], ACT_GELU_TANH);
+      break;
+    default:
+      break;
+  }
+}
+
 __device__ __forceinline__ uint64_t make_policy(uint32_t hint) {
   if (hint == 1) return policy_evict_first();
   if (hint == 2) return policy_evict_last();
@@ -742,12 +774,17 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           }
           if (row < row_end) {
             uint8_t* base = reinterpret_cast<uint8_t*>(p.out) + 2 * (w.batch * p.out_batch_stride);
+            if constexpr (T::EPI == EPI_BIAS) {
+#pragma unroll
+              for (int j = 0; j < CHUNK_COLS; ++j) v[j] += bias_v;
+            }
+            apply_act_chunk<CHUNK_COLS>(v, act);
 #pragma unroll
             for (int j = 0; j < CHUNK_COLS; ++j) {
               const int col = w.n0 + c32 * 32 + j;
               if (col < p.n) {
                 const long long at = static_cast<long long>(col) * p.out_ld + row;
-                store_elem(base, at, gate_elem(apply_act(v[j] + bias_v, act), at, col), is_bf16);
+                store_elem(base, at, gate_elem(v[j], at, col), is_bf16);
               }
             }
           }
@@ -763,10 +800,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               v[4 * j + 3] += b.w;
             }
           }
-          if (act != ACT_NONE) {
-#pragma unroll
-            for (int j = 0; j < CHUNK_COLS; ++j) v[j] = apply_act(v[j], act);
-          }
+          apply_act_chunk<CHUNK_COLS>(v, act);
           gate_chunk(v, c32);
           // Two 32-column chunks fill one 64-column (128-byte) store row.
           const int half = c32 & 1;
@@ -944,10 +978,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
                       for (int j = 0; j < 32; ++j) v[j] += smem_bias[bias_buf * BN + c32 * 32 + j];
                     }
-                    if (act != ACT_NONE) {
-#pragma unroll
-                      for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
-                    }
+                    apply_act_chunk<32>(v, act);
                     gate_chunk(v, c32);
                     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) +
                                    2 * (w.batch * p.out_batch_stride + static_cast<long long>(row) * p.out_ld + col0);
@@ -983,10 +1014,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   float bias_v = 0.0f;
                   if constexpr (T::EPI == EPI_BIAS) bias_v = load_elem(p.bias, row, is_bf16);
 #pragma unroll
+                  for (int j = 0; j < 4; ++j) v4[j] += bias_v;
+                  apply_act_chunk<4>(v4, act);
+#pragma unroll
                   for (int j = 0; j < 4; ++j) {
                     if (col + j < p.n) {
                       const long long at = static_cast<long long>(col + j) * p.out_ld + row;
-                      store_elem(base, at, gate_elem(apply_act(v4[j] + bias_v, act), at, col + j), is_bf16);
+                      store_elem(base, at, gate_elem(v4[j], at, col + j), is_bf16);
                     }
                   }
                 } else {
@@ -994,9 +1028,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
                     for (int j = 0; j < 4; ++j) v4[j] += load_elem(p.bias, col + j, is_bf16);
                   }
+                  apply_act_chunk<4>(v4, act);
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
-                    v4[j] = gate_elem(apply_act(v4[j], act), static_cast<long long>(row) * p.out_ld + col + j, row);
+                    v4[j] = gate_elem(v4[j], static_cast<long long>(row) * p.out_ld + col + j, row);
                   }
                   uint2 pk;
                   pk.x = pack2(v4[0], v4[1], is_bf16);
