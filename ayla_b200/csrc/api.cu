@@ -33,7 +33,7 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-constexpr int kMaxVariants = 64;
+constexpr int kMaxVariants = 96;
 constexpr int kMaxDevices = 64;
 
 struct Registry {
@@ -48,17 +48,25 @@ struct Registry {
     append_variants_act_cg1(entries, &count);
     append_variants_act_cg2(entries, &count);
     append_variants_act_trans(entries, &count);
+    append_variants_lean_cg1(entries, &count);
+    append_variants_lean_cg2(entries, &count);
+    append_variants_lean_trans(entries, &count);
   }
   int base_count = 0;  // the variants without the activation epilogue come first
-  const KernelEntry* find(int tile_n, int cta_group, int epilogue, int transposed, int activation = 0) const {
+  // `lean` asks for the variant without the k-split epilogues; where there is none the full
+  // variant serves.
+  const KernelEntry* find(int tile_n, int cta_group, int epilogue, int transposed, int activation = 0,
+                          int lean = 0) const {
+    const KernelEntry* full = nullptr;
     for (int i = 0; i < count; ++i) {
       const KernelEntry& e = entries[i];
       if (e.tile_n == tile_n && e.cta_group == cta_group && e.epilogue == epilogue &&
           e.transposed_out == transposed && e.activation == activation) {
-        return &e;
+        if (e.lean == lean) return &e;
+        if (e.lean == 0) full = &e;
       }
     }
-    return nullptr;
+    return full;
   }
 };
 
@@ -268,7 +276,8 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
               int64_t k, int sm_count, Plan* plan, int activation = 0) {
   const int transposed = c.swap_ab ? 1 : 0;
   const int tile_n = (epilogue == EPI_SWIGLU) ? 256 : c.tile_n;
-  const KernelEntry* e = registry().find(tile_n, c.cta_group, epilogue, transposed, activation != 0 ? 1 : 0);
+  const int lean = (c.split_k <= 1 && c.stream_k == 0) ? 1 : 0;
+  const KernelEntry* e = registry().find(tile_n, c.cta_group, epilogue, transposed, activation != 0 ? 1 : 0, lean);
   if (e == nullptr) {
     return fail(AYLA_B200_E_UNSUPPORTED, "no kernel variant tile_n=%d cta_group=%d epilogue=%d swap=%d",
                 tile_n, c.cta_group, epilogue, transposed);

@@ -102,8 +102,12 @@ struct KernelParams {
 #define AYLA_TRACE_END(slot)
 #endif
 
-template <int BN_, int CTA_GROUP_, int EPI_, bool TRANS_OUT_, int STAGES_, bool ACT_ = false>
+template <int BN_, int CTA_GROUP_, int EPI_, bool TRANS_OUT_, int STAGES_, bool ACT_ = false, bool LEAN_ = false>
 struct GemmTraits {
+  // LEAN: the kernel is compiled without the k-split epilogues (workspace and cluster forms) and
+  // serves the launches that do not split k.  The unused code is never executed, yet it costs a
+  // single-tile launch up to 1 us (instruction fetch), so those launches get a kernel without it.
+  static constexpr bool LEAN = LEAN_;
   // ACT: the epilogue applies the activation named in the launch parameters.  A separate set of
   // instantiations, so that the plain kernels carry none of that code (compiled in as a run-time
   // branch it cost the output-bound bmm 5 %).
@@ -501,7 +505,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
   // Cluster split-K: the cluster holds `csk` CTAs (CTA pairs when CG == 2), one per k-split
   // of the cluster's tile.
-  const int csk = (T::EPI != EPI_SWIGLU) ? p.cluster_split : 0;
+  const int csk = (T::EPI != EPI_SWIGLU && !T::LEAN) ? p.cluster_split : 0;
   const int csk_rank = csk > 0 ? static_cast<int>(cluster_ctarank()) / CG : 0;
   const int ctas_per_unit = CG * (csk > 0 ? csk : 1);
   const int first_unit = blockIdx.x / ctas_per_unit;
@@ -677,7 +681,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank, csk_rank);
     WorkUnit w;
     while (cursor.next(w)) {
-      const bool split_k = w.is_split;
+      const bool split_k = T::LEAN ? false : w.is_split;
 
       if constexpr (T::EPI == EPI_BIAS && !T::TRANS_OUT) {
         // Stage this tile's bias slice as fp32; double buffered so one barrier per

@@ -21,6 +21,7 @@ struct LaunchArgs {
 struct KernelEntry {
   int tile_n, cta_group, epilogue, transposed_out, stages, smem_bytes;
   int activation;  // 1 = the variant whose epilogue applies the launch's activation
+  int lean;        // 1 = the variant without the k-split epilogues
   const void* func;
   cudaError_t (*launch)(const LaunchArgs&);
 };
@@ -68,9 +69,9 @@ cudaError_t launch_variant(const LaunchArgs& a) {
   return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<T>, a.tm_a, a.tm_b, a.tm_b2, a.tm_d, a.p);
 }
 
-template <int BN, int CG, int EPI, bool TR, bool ACT = false>
+template <int BN, int CG, int EPI, bool TR, bool ACT = false, bool LEAN = false>
 KernelEntry make_entry() {
-  using T = GemmTraits<BN, CG, EPI, TR, max_stages<BN, CG, EPI, TR>(), ACT>;
+  using T = GemmTraits<BN, CG, EPI, TR, max_stages<BN, CG, EPI, TR>(), ACT, LEAN>;
   KernelEntry e;
   e.tile_n = BN;
   e.cta_group = CG;
@@ -79,6 +80,7 @@ KernelEntry make_entry() {
   e.stages = T::STAGES;
   e.smem_bytes = T::SMEM_BYTES;
   e.activation = ACT ? 1 : 0;
+  e.lean = LEAN ? 1 : 0;
   e.func = reinterpret_cast<const void*>(&gemm_sm100_kernel<T>);
   e.launch = &launch_variant<T>;
   return e;
@@ -92,5 +94,8 @@ void append_variants_swiglu(KernelEntry* out, int* count);
 void append_variants_act_cg1(KernelEntry* out, int* count);
 void append_variants_act_cg2(KernelEntry* out, int* count);
 void append_variants_act_trans(KernelEntry* out, int* count);
+void append_variants_lean_cg1(KernelEntry* out, int* count);
+void append_variants_lean_cg2(KernelEntry* out, int* count);
+void append_variants_lean_trans(KernelEntry* out, int* count);
 
 }  // namespace ayla_b200
