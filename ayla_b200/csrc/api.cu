@@ -33,7 +33,7 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-constexpr int kMaxVariants = 96;
+constexpr int kMaxVariants = 128;
 constexpr int kMaxDevices = 64;
 
 struct Registry {
@@ -51,6 +51,9 @@ struct Registry {
     append_variants_lean_cg1(entries, &count);
     append_variants_lean_cg2(entries, &count);
     append_variants_lean_trans(entries, &count);
+    append_variants_lean_act_cg1(entries, &count);
+    append_variants_lean_act_cg2(entries, &count);
+    append_variants_lean_act_trans(entries, &count);
   }
   int base_count = 0;  // the variants without the activation epilogue come first
   // `lean` asks for the variant without the k-split epilogues; where there is none the full

@@ -97,5 +97,8 @@ void append_variants_act_trans(KernelEntry* out, int* count);
 void append_variants_lean_cg1(KernelEntry* out, int* count);
 void append_variants_lean_cg2(KernelEntry* out, int* count);
 void append_variants_lean_trans(KernelEntry* out, int* count);
+void append_variants_lean_act_cg1(KernelEntry* out, int* count);
+void append_variants_lean_act_cg2(KernelEntry* out, int* count);
+void append_variants_lean_act_trans(KernelEntry* out, int* count);
 
 }  // namespace ayla_b200
