@@ -52,9 +52,10 @@ WORKLOAD = "C1 mm bf16 4096x4096x4096"
 M = N = K = 4096
 FLOPS = 2.0 * M * N * K
 ALGO_BYTES = 2.0 * (M * K + N * K + M * N)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
-# summarised in profiles/ (None until measured).
-NCU_TRAFFIC_BYTES = 100.7e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures
+# summarised in profiles/gemm_sm100_c1_mm_4096.md (100.4-102.6 MB over four captured launches;
+# this is the latest one).
+NCU_TRAFFIC_BYTES = 102.5e6
 
 
 def read_peaks() -> dict:
