@@ -148,3 +148,19 @@ def test_activation_ops_are_registered_with_the_plain_ops_signature():
     assert op(bias, a, bt, out) is None
     with pytest.raises(ValueError, match="unsupported GEMM activation"):
         gemm_act_op("mm", "tanh", "float16")
+
+
+def test_row_factor_op_is_registered_with_one_more_operand():
+    from ayla_b200 import gemm_act_rowmul_op
+    from ayla_b200.gemm_jit import gemm_jit_compiler
+
+    op = gemm_act_rowmul_op("mm", "none", "bfloat16")
+    assert op is torch.ops.ayla.jit_mm_rowmul_bf16.default
+    assert str(op._schema) == "ayla::jit_mm_rowmul_bf16(Tensor arg0, Tensor arg1, Tensor arg2, Tensor(a3!) arg3) -> ()"
+    assert gemm_act_rowmul_op("bmm", "silu", "float16") is torch.ops.ayla.jit_bmm_silu_rowmul_f16.default
+    a = torch.empty(8, 32, dtype=torch.bfloat16, device="meta")
+    bt = torch.empty(16, 32, dtype=torch.bfloat16, device="meta")
+    out = torch.empty(8, 16, dtype=torch.bfloat16, device="meta")
+    assert op(a, bt, torch.empty(8, 1, dtype=torch.bfloat16, device="meta"), out) is None
+    with pytest.raises(ValueError, match="unsupported gate"):
+        gemm_jit_compiler("mm", "bfloat16", "none", gated="column")
