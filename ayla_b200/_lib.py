@@ -171,6 +171,29 @@ def check(code: int) -> None:
     raise AylaB200Error(code, message)
 
 
+class StatusWord:
+    """The status word of a launcher: a uint32 in pinned host memory that the kernels write
+    through its device mapping (under unified addressing pinned host memory has the same
+    address on the device) and the host reads without synchronising.  A kernel whose bounded
+    wait gave up leaves a non-zero code there; the launcher looks at the word before its next
+    launch, so a timed-out launch is reported at the next call of that shape instead of
+    silently poisoning later ones."""
+
+    def __init__(self):
+        import torch
+
+        self.tensor = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.ptr = self.tensor.data_ptr()
+        self._word = ctypes.c_uint32.from_address(self.ptr)
+
+    def peek(self) -> int:
+        """The current value, read from host memory: no device synchronisation."""
+        return self._word.value
+
+    def clear(self) -> None:
+        self._word.value = 0
+
+
 def init(device: int) -> None:
     """Per-device set-up; must first happen outside CUDA-graph capture."""
     if device in _initialised_devices:

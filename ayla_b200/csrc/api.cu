@@ -321,6 +321,10 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
     const int64_t min_share = plan->k_blocks < 4 ? plan->k_blocks : 4;
     if (share < min_share) share = min_share;
     ctas = ceil_div(total_kb, share);
+    if (ctas * c.cta_group > kMaxSplitKTiles) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "stream_k over %lld CTAs (limit %d arrival counters)",
+                  (long long)(ctas * c.cta_group), kMaxSplitKTiles);
+    }
     plan->stream_k = 1;
     plan->kb_per_cta = static_cast<int>(share);
     plan->splits = 1;
@@ -623,7 +627,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   }
 #ifdef AYLA_B200_TRACE
   // Tuning builds: a schedule that needs no scratch lends the workspace to the per-CTA cycle counters.
-  if (plan.slabs == 0 && workspace != nullptr && workspace_bytes >= (4096 + static_cast<size_t>(plan.grid) * 8) * 8) {
+  if (plan.slabs == 0 && workspace != nullptr && workspace_bytes >= (4096 + static_cast<size_t>(plan.grid) * 16) * 8) {
     p.trace = reinterpret_cast<long long*>(workspace);
   }
 #endif
@@ -717,6 +721,14 @@ int ayla_b200_init(int device) {
       }
     }
     if (rc) break;
+    {
+      // Resolve the built-in scratch array here as well, with `device` current: the query loads the
+      // library's device image if nothing has yet, which is better done at set-up than inside the
+      // first ayla_b200_gemm_static_scratch call.
+      void* scratch = nullptr;
+      rc = static_scratch_for_current_device(device, &scratch);
+      if (rc) break;
+    }
     g_devices[device].sm_count = prop.multiProcessorCount;
     g_devices[device].ready.store(true, std::memory_order_release);
   } while (false);

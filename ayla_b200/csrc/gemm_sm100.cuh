@@ -435,8 +435,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #ifdef AYLA_B200_TRACE
   // Timeline of this CTA in globaltimer nanoseconds: entry, set-up done, first operands
   // landed, last MMA committed, epilogue done, exit.
-  long long* stamps = (p.trace != nullptr) ? p.trace + 4096 + blockIdx.x * 8 : nullptr;
-  if (stamps != nullptr && threadIdx.x == 0) stamps[0] = static_cast<long long>(global_timer_ns());
+  // Slots: 0 entry, 1 set-up done, 2 first operands landed, 3 last MMA committed, 4 epilogue done, 5 exit,
+  // 6/7 cluster split-K barriers, 8 SM id, 9-11 a quarter / half / three quarters of the CTA's first unit
+  // issued, 12 first TMA load issued, 13 epilogue saw the first finished accumulator.
+  long long* stamps = (p.trace != nullptr) ? p.trace + 4096 + blockIdx.x * 16 : nullptr;
+  if (stamps != nullptr && threadIdx.x == 0) {
+    stamps[0] = static_cast<long long>(global_timer_ns());
+    uint32_t smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    stamps[8] = static_cast<long long>(smid) + 1;
+  }
 #endif
   // A CTA pair is two CTAs whose ranks in the cluster differ in the last bit; with cluster
   // split-K a cluster holds several pairs, so the leader is the even rank of the pair,
@@ -550,6 +558,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
         if (issuer) {
+#ifdef AYLA_B200_TRACE
+          if (stamps != nullptr && stamps[12] == 0) stamps[12] = static_cast<long long>(global_timer_ns());
+#endif
           const uint32_t full_bar = full_bar0 + stage * 8;
           if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, p.stage_tx);
           const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
@@ -607,6 +618,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (stamps != nullptr && lane == 0 && !first_operands_stamped) {
             stamps[2] = static_cast<long long>(global_timer_ns());
             first_operands_stamped = true;
+          }
+          if (stamps != nullptr && lane == 0 && stamps[3] == 0) {
+            const int span = w.kb1 - w.kb0, done = kb - w.kb0;
+            for (int qd = 1; qd <= 3; ++qd) {
+              if (span >= 4 && done == qd * span / 4 && stamps[8 + qd] == 0) {
+                stamps[8 + qd] = static_cast<long long>(global_timer_ns());
+              }
+            }
           }
 #endif
           tc_fence_after_sync();
@@ -695,6 +714,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
 
       AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL))
+#ifdef AYLA_B200_TRACE
+      if (stamps != nullptr && warp == 2 && lane == 0 && stamps[13] == 0) stamps[13] = static_cast<long long>(global_timer_ns());
+#endif
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 

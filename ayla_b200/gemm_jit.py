@@ -187,11 +187,18 @@ def _fallback_schedule(operation: str, dtype: str, m: int, n: int, k: int,
 class GemmLauncher:
     """One specialised ``(operation, dtype, shape, device)`` launch.
 
-    Owns the split-K workspace and the device status word of its shape; both are
+    Owns the split-K workspace and the status word of its shape; both are
     allocated here, at specialisation time, so that a launch itself allocates
     nothing and can be captured in a CUDA graph.  Two launches of the same shape
     that overlap on different streams would share that workspace; callers that
     do so must serialise them.
+
+    The status word lives in pinned host memory (``_lib.StatusWord``): every call reads it
+    before launching, without synchronising, and raises ``RuntimeError`` if an earlier
+    launch of this shape ran into one of the kernel's bounded waits; the split-K arrival
+    counters that launch may have left dirty are cleared first, so the call after the
+    error is correct again.  ``check_status()`` does the same after a synchronise, and
+    ``AYLA_B200_DEBUG=1`` calls it after every launch.
     """
 
     def __init__(self, operation: str, dtype: str, batch: int, m: int, n: int, k: int,
@@ -208,9 +215,9 @@ class GemmLauncher:
             _lib.init(index)
         need = _lib.workspace_bytes(self.config, operation, batch, m, n, k)
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=device) if need else None
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = _lib.StatusWord()
         self._ws_ptr = self.workspace.data_ptr() if self.workspace is not None else 0
-        self._status_ptr = self.status.data_ptr()
+        self._status_ptr = self.status.ptr
         self._debug = bool(os.environ.get("AYLA_B200_DEBUG"))
         # Everything that does not change from call to call, converted for the C call once.
         import ctypes
@@ -233,23 +240,38 @@ class GemmLauncher:
             mul_ptr = mul.data_ptr()
         else:
             a, bt, out = tensors
-        code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), mul_ptr, out.data_ptr(), *self._tail,
-                           torch.cuda.current_stream(self._device_index).cuda_stream)
+        if self.status.peek():
+            self._report_timeout()
+        # The library launches on the current device (the reference's launcher guards the device
+        # the same way, ayla/ptx_runtime.py:268-275).
+        if torch.cuda.current_device() != self._device_index:
+            with torch.cuda.device(self._device_index):
+                code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), mul_ptr, out.data_ptr(),
+                                   *self._tail, torch.cuda.current_stream(self._device_index).cuda_stream)
+        else:
+            code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), mul_ptr, out.data_ptr(),
+                               *self._tail, torch.cuda.current_stream(self._device_index).cuda_stream)
         if code:
             _lib.check(code)
         if self._debug:
             self.check_status()
 
+    def _report_timeout(self) -> None:
+        code = self.status.peek()
+        with torch.cuda.device(self._device_index):
+            torch.cuda.current_stream().synchronize()  # nothing of the failed launch is still running
+            if self.workspace is not None:
+                self.workspace.zero_()  # arrival counters a timed-out k-split leaves behind
+        self.status.clear()
+        raise RuntimeError(
+            f"jit_{self.operation}: device wait timed out (code {code & 0xFF}, CTA {code >> 8})"
+        )
+
     def check_status(self) -> None:
         """Synchronise and raise if one of the kernel's bounded waits gave up."""
-        code = int(self.status.item())
-        if code:
-            self.status.zero_()
-            if self.workspace is not None:
-                self.workspace.zero_()
-            raise RuntimeError(
-                f"jit_{self.operation}: device wait timed out (code {code & 0xFF}, CTA {code >> 8})"
-            )
+        torch.cuda.synchronize(self._device_index)
+        if self.status.peek():
+            self._report_timeout()
 
 
 def _op_name(operation: str, dtype: str, activation: str = "none", gated: bool | str = False) -> str:

@@ -28,23 +28,32 @@ class SwigluLauncher:
         with torch.cuda.device(index):
             _lib.init(index)
         self.config = _lib.Config.from_dict(config) if config is not None else None
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self._status_ptr = self.status.data_ptr()
+        self.status = _lib.StatusWord()  # pinned host word: read before every launch without a synchronise
+        self._status_ptr = self.status.ptr
+        self._device_index = index
         self._debug = bool(os.environ.get("AYLA_B200_DEBUG"))
 
     def __call__(self, x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
                  out: torch.Tensor) -> None:
-        _lib.swiglu(self.dtype, x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(),
-                    self.m, self.n, self.k, self.config, self._status_ptr,
-                    torch.cuda.current_stream(self.device).cuda_stream)
+        if self.status.peek():
+            self._report_timeout()
+        with torch.cuda.device(self._device_index):
+            _lib.swiglu(self.dtype, x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(),
+                        self.m, self.n, self.k, self.config, self._status_ptr,
+                        torch.cuda.current_stream(self._device_index).cuda_stream)
         if self._debug:
             self.check_status()
 
+    def _report_timeout(self) -> None:
+        code = self.status.peek()
+        self.status.clear()
+        raise RuntimeError(f"swiglu: device wait timed out (code {code & 0xFF}, CTA {code >> 8})")
+
     def check_status(self) -> None:
-        code = int(self.status.item())
-        if code:
-            self.status.zero_()
-            raise RuntimeError(f"swiglu: device wait timed out (code {code & 0xFF}, CTA {code >> 8})")
+        """Synchronise and raise if one of the kernel's bounded waits gave up."""
+        torch.cuda.synchronize(self._device_index)
+        if self.status.peek():
+            self._report_timeout()
 
 
 def swiglu_compiler(dtype: str) -> ShapeSpecializingJITCompiler:

@@ -24,7 +24,7 @@ import torch
 from torch._inductor import config as inductor_config
 from torch._inductor.custom_graph_pass import CustomGraphPass, get_hash_for_files
 
-from .gemm_jit import (_SHORT_DTYPES, _TORCH_DTYPES, _op_name, gemm_jit_compiler, gemm_op,
+from .gemm_jit import (_SHORT_DTYPES, _TORCH_DTYPES, ACTIVATIONS, _op_name, gemm_jit_compiler, gemm_op,
                        select_gemm_schedule)
 from .torch_custom_call import DEFAULT_NAMESPACE, OperandKind, make_torch_custom_call
 
@@ -32,12 +32,17 @@ aten = torch.ops.aten
 _DTYPE_NAMES = {torch.float16: "float16", torch.bfloat16: "bfloat16"}
 
 
-@cache
 def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE,
                activation: str = "none", gated: bool = False) -> torch._ops.OpOverload:
     """Functional form ``(bias?, a, bt[, mul]) -> out`` of ``gemm_op`` / ``gemm_act_op`` /
     ``gemm_act_mul_op`` (the result is allocated by the op), the form a functional FX graph can
-    hold.  Counterpart of the reference's allocating ops (ayla/gemm_collection/dynamic_m.py:90-121)."""
+    hold.  Counterpart of the reference's allocating ops (ayla/gemm_collection/dynamic_m.py:90-121).
+    Cached: one op per distinct argument tuple, however the defaults were spelled."""
+    return _gemm_fn_op(operation, dtype, namespace, activation, bool(gated))
+
+
+@cache
+def _gemm_fn_op(operation: str, dtype: str, namespace: str, activation: str, gated: bool) -> torch._ops.OpOverload:
     compiler = gemm_jit_compiler(operation, dtype, activation, gated)
 
     def infer(*inputs: torch.Tensor):
@@ -387,44 +392,90 @@ def route_gated(graph: torch.fx.Graph) -> int:
     return rewritten
 
 
+def _concat_halves(gate, up):
+    """If ``gate`` and ``up`` are the two column halves of one 2-D ``aten.mm`` result, return
+    (mm node, half width, nodes between the mm and the halves); else None.  Two spellings occur:
+    ``chunk``/``split`` (``aten.split.Tensor`` + ``getitem`` 0 and 1) and the pair of slices
+    ``aten.slice.Tensor(mm, 1, 0, n)`` / ``aten.slice.Tensor(mm, 1, n, end)`` that a captured
+    decoder block holds (benchmarks/bench_torch_compile/corpus/muse_glimmer_block.py:42-50 of the
+    reference)."""
+    import operator
+
+    if _is_call(gate, operator.getitem) and _is_call(up, operator.getitem):
+        split = gate.args[0]
+        if not (up.args[0] is split and gate.args[1] == 0 and up.args[1] == 1):
+            return None
+        if not _is_call(split, aten.split.Tensor) or not _is_call(split.args[0], aten.mm.default):
+            return None
+        mm = split.args[0]
+        mv = _val(mm)
+        if mv is None or mv.dim() != 2:
+            return None
+        n2 = mv.shape[-1]
+        dim = split.args[2] if len(split.args) > 2 else 0
+        if not isinstance(n2, int) or n2 % 2 or split.args[1] != n2 // 2 or dim not in (-1, 1):
+            return None
+        if not (_only_used_by(mm, {split}) and _only_used_by(split, {gate, up})):
+            return None
+        return mm, n2 // 2, [split]
+    if _is_call(gate, aten.slice.Tensor) and _is_call(up, aten.slice.Tensor):
+        mm = gate.args[0]
+        if up.args[0] is not mm or not _is_call(mm, aten.mm.default):
+            return None
+        mv = _val(mm)
+        if mv is None or mv.dim() != 2 or not isinstance(mv.shape[-1], int) or mv.shape[-1] % 2:
+            return None
+        n2 = mv.shape[-1]
+        half = n2 // 2
+
+        def bounds(node):
+            dim = node.args[1] if len(node.args) > 1 else 0
+            start = node.args[2] if len(node.args) > 2 else None
+            end = node.args[3] if len(node.args) > 3 else None
+            step = node.args[4] if len(node.args) > 4 else 1
+            if dim not in (1, -1) or step != 1:
+                return None
+            start = 0 if start is None else start
+            end = n2 if end is None else end
+            if not isinstance(start, int) or not isinstance(end, int):
+                return None
+            return start, min(end, n2)
+
+        if bounds(gate) != (0, half) or bounds(up) != (half, n2):
+            return None
+        if not _only_used_by(mm, {gate, up}):
+            return None
+        return mm, half, []
+    return None
+
+
 def route_swiglu_concat(graph: torch.fx.Graph) -> int:
     """Rewrite SwiGLU on a concatenated weight, ``g, u = (x @ w.T).chunk(2, -1); silu(g) * u``
     with ``w`` of shape ``[2 n, k]`` (the form real decoder blocks use,
     benchmarks/muse_glimmer_block.py:41-50 of the reference), into the fused SwiGLU op on the
-    two row halves of ``w``."""
-    import operator
-
+    two row halves of ``w``.  The halves may be spelled as ``split`` + ``getitem`` or as two
+    ``slice`` nodes of the product."""
     rewritten = 0
     for node in list(graph.nodes):
         if not _is_call(node, aten.mul.Tensor) or len(node.args) != 2:
             continue
         for act, up in (node.args, node.args[::-1]):
             found = _silu_source(act)
-            if found is None or not _is_call(up, operator.getitem):
+            if found is None or not isinstance(up, torch.fx.Node):
                 continue
             gate, chain = found
-            if not (_is_call(gate, operator.getitem) and gate.args[0] is up.args[0]
-                    and gate.args[1] == 0 and up.args[1] == 1):
+            halves = _concat_halves(gate, up)
+            if halves is None:
                 continue
-            split = gate.args[0]
-            if not _is_call(split, aten.split.Tensor) or not _is_call(split.args[0], aten.mm.default):
-                continue
-            mm = split.args[0]
-            mv = _val(mm)
-            if mv is None or mv.dim() != 2:
-                continue
-            n2 = mv.shape[-1]
-            dim = split.args[2] if len(split.args) > 2 else 0
-            if not isinstance(n2, int) or n2 % 2 or split.args[1] != n2 // 2 or dim not in (-1, 1):
-                continue
+            mm, half, between = halves
+            n2 = 2 * half
             x, w_t = mm.args
-            half = n2 // 2
             claim = _claim("mm", x, w_t)
             if claim is None or half % 8:
                 continue
-            members = set(chain) | {node, split, gate, up}
-            if not (_only_used_by(mm, {split}) and _only_used_by(split, {gate, up}) and _only_used_by(up, {node})
-                    and _only_used_by(gate, members) and all(_only_used_by(n, members) for n in chain)):
+            members = set(chain) | {node, gate, up, *between}
+            if not (_only_used_by(up, {node}) and _only_used_by(gate, members)
+                    and all(_only_used_by(n, members) for n in chain)):
                 continue
             dtype = claim[0]
             with graph.inserting_before(node):
@@ -506,22 +557,33 @@ class AylaRoutingPass(CustomGraphPass):
 _installed: AylaRoutingPass | None = None
 
 
+def emittable_ops() -> list[tuple]:
+    """Every functional op a rewrite of this pass can put into a graph, as argument tuples of
+    ``gemm_fn_op`` (``("swiglu", dtype)`` for the SwiGLU op): each operation and dtype, plain,
+    with each activation ``_activation_source`` can name, and each of those with a gate."""
+    ops: list[tuple] = []
+    for dtype in _TORCH_DTYPES:
+        ops.append(("swiglu", dtype))
+        for operation in ("mm", "addmm", "bmm"):
+            for activation in ACTIVATIONS:
+                ops.append((operation, dtype, DEFAULT_NAMESPACE, activation, False))
+                ops.append((operation, dtype, DEFAULT_NAMESPACE, activation, True))
+    return ops
+
+
 def install() -> None:
     """Claim the GEMMs.  Idempotent."""
     global _installed
-    # Register the ops up front: a cached graph can call one without this process ever
-    # running the pass that would create it.
+    # Register every op the pass can emit up front: on a hit in Inductor's code cache the pass does
+    # not run in this process, and the cached code calls torch.ops.ayla.* by name.
     for operation in ("mm", "addmm", "bmm"):
         for dtype in _TORCH_DTYPES:
             gemm_op(operation, dtype)
-            gemm_fn_op(operation, dtype)
-    for dtype in _TORCH_DTYPES:
-        swiglu_fn_op(dtype)
-        for operation in ("mm", "addmm", "bmm"):
-            for activation in ("relu", "sigmoid", "silu", "gelu"):
-                gemm_fn_op(operation, dtype, DEFAULT_NAMESPACE, activation)
-            for activation in ("none", "sigmoid", "silu"):
-                gemm_fn_op(operation, dtype, DEFAULT_NAMESPACE, activation, True)
+    for spec in emittable_ops():
+        if spec[0] == "swiglu":
+            swiglu_fn_op(spec[1])
+        else:
+            gemm_fn_op(*spec)
     current = inductor_config.post_grad_custom_post_pass
     if _installed is not None and current is _installed:
         return

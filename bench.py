@@ -1,6 +1,7 @@
 """Benchmark of the GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--suite]
+    python bench.py --case C1 [--launches 6] [--schedule '{"tile_n":256,...}'] [--torch]
 
 Default arm: one JSON line for the headline workload, bf16 ``mm`` with
 M = N = K = 4096 (``out = a @ bt.T``), one step = one launch through the C ABI:
@@ -10,10 +11,22 @@ M = N = K = 4096 (``out = a @ bt.T``), one step = one launch through the C ABI:
 * ``e2e``       the same metric through ``gemm_op`` with HOST operands: every step
                 copies a and bt from pinned host memory, launches, and copies out back;
 * ``roofline``  tensor-pipe roofline of the GEMM kernel against the measured cuBLAS
-                bf16 peak in MEASURED_PEAKS.json;
+                bf16 burst peak in MEASURED_PEAKS.json (the sustained figure only when the
+                timed region itself lasts a second or more; both fractions are printed);
+* ``vs_cublas`` cuBLAS (torch.mm) on the same operand sets, timed in the same regime:
+                blocks of launches of the two arms alternating, starting arm rotating;
 * ``cpu_baseline`` the CPU oracle (PyTorch fp32 mm of the same operands) timed on the
                 host cores;
-* ``extra``     the fused SwiGLU config and cuBLAS (torch.mm) on the same operands.
+* ``extra``     the fused SwiGLU config, and ``extra.hbm``: weight-streaming shapes
+                (M = 8 and 64 on 14336x4096 and 4096x4096 weights) with operands rotating
+                past L2, each with its HBM roofline.
+
+The schedule timed is the one ``gemm_op`` runs for the shape
+(``select_gemm_schedule(...).builder_config``).
+
+``--case`` launches one benchmark config a few times and exits: the command that is put
+under ``ncu`` (configs C1, C2a, C2b, C3a, C3b, C4, or ``mm:M,N,K`` / ``addmm:M,N,K`` /
+``bmm:B,M,N,K``; ``--torch`` launches the cuBLAS counterpart instead).
 
 ``--impl reference`` times the reference's CPU path for this workload: the reference has
 no CPU kernel of its own, its tests define the result as PyTorch's fp32 matmul
@@ -52,9 +65,8 @@ WORKLOAD = "C1 mm bf16 4096x4096x4096"
 M = N = K = 4096
 FLOPS = 2.0 * M * N * K
 ALGO_BYTES = 2.0 * (M * K + N * K + M * N)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures
-# summarised in profiles/gemm_sm100_c1_mm_4096.md (100.4-102.6 MB over four captured launches;
-# this is the latest one).
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from
+# an ncu capture (--set full, one launch; 100.4-102.6 MB over four captured launches).
 NCU_TRAFFIC_BYTES = 102.5e6
 
 
@@ -141,6 +153,151 @@ def cuda_time_ms(fn, steps: int, stream=None) -> float:
     stop.record()
     torch.cuda.synchronize()
     return start.elapsed_time(stop) / steps
+
+
+def gpu_numa_cpus(device_index: int) -> tuple[int | None, set[int]]:
+    """(NUMA node, CPUs of that node) of a GPU, read from sysfs through its PCI address."""
+    props = torch.cuda.get_device_properties(device_index)
+    bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+    node = int(Path(f"/sys/bus/pci/devices/{bdf}/numa_node").read_text().strip())
+    if node < 0:
+        return None, set()
+    cpus: set[int] = set()
+    for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return node, cpus
+
+
+class NumaLocal:
+    """While active, this process runs on the CPUs of the GPU's NUMA node, so host buffers pinned
+    inside the block get their pages there (first touch).  The previous affinity is restored on
+    exit; nothing outside this process is changed."""
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.info: dict = {"node": None, "bound": False}
+        self._previous = None
+
+    def __enter__(self):
+        try:
+            node, cpus = gpu_numa_cpus(self.device_index)
+            self._previous = os.sched_getaffinity(0)
+            usable = cpus & self._previous
+            self.info["node"] = node
+            if usable:
+                os.sched_setaffinity(0, usable)
+                self.info.update(bound=True, cpus=len(usable))
+        except (OSError, ValueError, AttributeError) as exc:
+            self.info["error"] = f"{type(exc).__name__}: {exc}"
+        return self
+
+    def __exit__(self, *exc):
+        if self._previous is not None and self.info.get("bound"):
+            os.sched_setaffinity(0, self._previous)
+
+
+def interleaved_blocks(arms: dict, block: int, rounds: int) -> dict:
+    """Milliseconds per launch of each arm ``fn(i)``: the arms run in alternating blocks of `block`
+    launches, the starting arm rotating from round to round, every block bracketed by CUDA events on
+    the current stream -- so both arms see the same clocks, power state and cache contents."""
+    names = list(arms)
+    total = {name: 0.0 for name in names}
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for r in range(rounds):
+        order = names[r % len(names):] + names[:r % len(names)]
+        for name in order:
+            fn = arms[name]
+            start.record()
+            for i in range(block):
+                fn(i)
+            stop.record()
+            stop.synchronize()
+            total[name] += start.elapsed_time(stop)
+    return {name: total[name] / (block * rounds) for name in names}
+
+
+CASES = {
+    "C1": ("mm", 1, 4096, 4096, 4096),
+    "C2a": ("addmm", 1, 8192, 768, 768),
+    "C2b": ("addmm", 1, 256, 1024, 16384),
+    "C3a": ("bmm", 64, 2048, 2048, 128),
+    "C3b": ("bmm", 64, 2048, 128, 2048),
+    "C4": ("swiglu", 1, 8192, 14336, 4096),
+}
+
+
+def run_case(args) -> None:
+    """Launch one config ``--launches`` times and exit (random inputs, nothing checked): the
+    command profiled with ncu."""
+    from ayla_b200 import _lib
+    from ayla_b200.gemm_jit import select_gemm_schedule
+
+    if args.case in CASES:
+        op, batch, m, n, k = CASES[args.case]
+    else:
+        op, dims = args.case.split(":")
+        values = [int(v) for v in dims.split(",")]
+        batch, (m, n, k) = (values[0], values[1:]) if op == "bmm" else (1, values)
+    dev = "cuda:0"
+    _lib.init(0)
+    td = torch.bfloat16 if args.dtype == "bfloat16" else torch.float16
+    stream = torch.cuda.current_stream().cuda_stream
+    cfg = _lib.Config.from_dict(json.loads(args.schedule)) if args.schedule else None
+    if op == "swiglu":
+        x = torch.randn(m, k, device=dev).to(td)
+        wg = (torch.randn(n, k, device=dev) * 0.02).to(td)
+        wu = (torch.randn(n, k, device=dev) * 0.02).to(td)
+        out = torch.empty(m, n, device=dev, dtype=td)
+        for _ in range(args.launches):
+            if args.torch:
+                torch.mul(torch.nn.functional.silu(torch.mm(x, wg.t())), torch.mm(x, wu.t()), out=out)
+            else:
+                _lib.swiglu(args.dtype, x.data_ptr(), wg.data_ptr(), wu.data_ptr(), out.data_ptr(), m, n, k, cfg,
+                            0, stream)
+    else:
+        lead = (batch,) if op == "bmm" else ()
+        a = torch.randn((*lead, m, k), device=dev).to(td)
+        bt = (torch.randn((*lead, n, k), device=dev) * k ** -0.5).to(td)
+        bias = torch.randn(n, device=dev).to(td)
+        out = torch.empty((*lead, m, n), device=dev, dtype=td)
+        if cfg is None:
+            cfg = _lib.Config.from_dict(select_gemm_schedule(op, args.dtype, m, n, k, batch).builder_config)
+        need = _lib.workspace_bytes(cfg, op, batch, m, n, k)
+        ws = torch.zeros(max(need, 16), dtype=torch.uint8, device=dev)
+        for _ in range(args.launches):
+            if args.torch:
+                if op == "mm":
+                    torch.mm(a, bt.t(), out=out)
+                elif op == "addmm":
+                    torch.addmm(bias, a, bt.t(), out=out)
+                else:
+                    torch.bmm(a, bt.transpose(1, 2), out=out)
+            else:
+                _lib.gemm(op, args.dtype, bias.data_ptr() if op == "addmm" else 0, a.data_ptr(), bt.data_ptr(),
+                          out.data_ptr(), batch, m, n, k, cfg, ws.data_ptr(), ws.numel(), 0, stream)
+    torch.cuda.synchronize()
+    arm = "torch" if args.torch else "ayla_b200"
+    print(f"{args.case}: {args.launches} {arm} launches of {op} {batch}x{m}x{n}x{k} done")
+
+
+def hbm_rows(peaks: dict) -> list[dict]:
+    """Weight-streaming shapes (HBM-bound: the weight is read once per launch): graph replay with
+    operand sets rotating through more than 2.5x L2, cuBLAS interleaved (``ayla_b200.suite``)."""
+    from ayla_b200.suite import measure_gemm
+
+    rows = []
+    for m, n, k in ((8, 14336, 4096), (64, 14336, 4096), (8, 4096, 4096), (64, 4096, 4096)):
+        row = measure_gemm("mm", "bfloat16", 1, m, n, k, peaks, rounds=7)
+        nbytes = 2.0 * (m * k + n * k + m * n)
+        rows.append({
+            "workload": f"mm bf16 M={m} N={n} K={k}", "us": row["ms"] * 1e3, "torch_us": row["torch_ms"] * 1e3,
+            "vs_cublas": row["speedup_vs_torch"], "schedule": row["schedule"],
+            "roofline": {"bound": "hbm", "achieved": row["gbs"], "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": row["gbs"] / peaks["hbm"], "algorithmic_bytes": nbytes,
+                         "peak_source": f"{peaks['source']} HBM copy bandwidth"},
+        })
+    return rows
 
 
 def dist_setup(n_gpus: int):
@@ -279,6 +436,11 @@ def main() -> None:
     parser.add_argument("--suite", action="store_true")
     parser.add_argument("--suite-out", default="results/suite.json")
     parser.add_argument("--no-extra", action="store_true")
+    parser.add_argument("--case", default=None, help="launch this config --launches times and exit (for ncu)")
+    parser.add_argument("--launches", type=int, default=6)
+    parser.add_argument("--schedule", default=None, help="JSON schedule for --case (default: the table's)")
+    parser.add_argument("--dtype", default="bfloat16")
+    parser.add_argument("--torch", action="store_true", help="--case launches the cuBLAS counterpart instead")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -288,6 +450,9 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path "
                          "(use --impl reference for the CPU baseline)")
+    if args.case:
+        run_case(args)
+        return
 
     rank, world, local = dist_setup(args.gpus)
     from ayla_b200 import _lib, gemm_op
@@ -305,36 +470,7 @@ def main() -> None:
     stream = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(1, dtype=torch.int32, device=device)
 
-    # The table ranks schedules by short graph-replayed bursts; this loop runs for seconds under the
-    # power cap, where the L2 eviction hints that keep operands resident can rank differently.  So,
-    # as part of the warm-up, the schedules measured for this shape are timed in that regime and the
-    # fastest is the one timed below (reported in config.schedule).
-    from ayla_b200.gemm_jit import measured_gemm_configs
-
-    candidates = [_lib.Config.from_dict({key: c[key] for key in _lib.Config.FIELDS}) for c in
-                  measured_gemm_configs("mm", "bfloat16", M, N, K)]
-    schedule_choice = "the library's schedule for this shape"
-    if len(candidates) > 1:
-        def runner(candidate):
-            def run(i):
-                a, bt, out = sets[i % len(sets)]
-                _lib.gemm("mm", "bfloat16", 0, a.data_ptr(), bt.data_ptr(), out.data_ptr(), 1, M, N, K, candidate,
-                          0, 0, status.data_ptr(), stream)
-            return run
-
-        runners = [runner(c) for c in candidates]
-        # Bring the GPU to its power-capped state first, then time the candidates in three rounds with
-        # a rotating order, so that none is measured at the higher clocks of a cold start.
-        cuda_time_ms(runners[0], 1500)
-        trials = [0.0] * len(candidates)
-        for round_index in range(3):
-            for j in range(len(candidates)):
-                which = (j + round_index) % len(candidates)
-                trials[which] += cuda_time_ms(runners[which], 300) / 3.0
-        trials = max_over_ranks_list(trials, world)
-        cfg = candidates[min(range(len(trials)), key=trials.__getitem__)]
-        schedule_choice = (f"fastest of the {len(candidates)} schedules measured for this shape, 3 x 300 warm "
-                           f"launches each under the power cap ({', '.join(f'{t * 1e3:.1f}' for t in trials)} us)")
+    schedule_choice = "select_gemm_schedule('mm', 'bfloat16', 4096, 4096, 4096).builder_config, the schedule gemm_op runs"
 
     def step(i):
         a, bt, out = sets[i % len(sets)]
@@ -369,14 +505,36 @@ def main() -> None:
     if int(status.item()) != 0:
         raise SystemExit(f"device status {int(status.item()):#x}: a bounded wait gave up")
 
+    # ---- cuBLAS on the same operand sets, in the same regime: straight after the timed loop (the
+    # GPU is as warm and as power-capped as it was there), blocks of launches of the two arms
+    # alternating, the starting arm rotating.
+    vs_cublas = None
+    if world == 1 and not args.no_extra:
+        def cublas(i):
+            a, bt, out = sets[i % len(sets)]
+            torch.mm(a, bt.t(), out=out)
+
+        for i in range(3):
+            cublas(i)
+        block = max(50, min(250, args.steps // 4))
+        per_arm = interleaved_blocks({"ours": step, "cublas": cublas}, block, rounds=6)
+        vs_cublas = {"ratio": per_arm["cublas"] / per_arm["ours"], "ours_ms": per_arm["ours"],
+                     "cublas_ms": per_arm["cublas"], "ours_tflops": FLOPS / per_arm["ours"] / 1e9,
+                     "cublas_tflops": FLOPS / per_arm["cublas"] / 1e9,
+                     "protocol": f"6 rounds of alternating blocks of {block} launches per arm, starting arm "
+                                 "rotating, CUDA events per block, same operand sets, run directly after the timed loop"}
+
     # ---- end to end through the public op with host operands: every step copies its a and bt in
     # from pinned host memory and its result back out.  The three legs run on three streams over
     # two device buffer sets, so the copy-in of step i+1 and the copy-out of step i-1 overlap the
     # GEMM of step i (PCIe is full duplex); events keep each buffer's copy-in -> GEMM -> copy-out order.
     op = gemm_op("mm", "bfloat16")
-    host_a = a0.pin_memory()
-    host_bt = bt0.pin_memory()
-    host_outs = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    # The pinned buffers are allocated while this process runs on the CPUs of the GPU's own NUMA
+    # node, so that with one process per GPU every rank copies from and to memory next to its GPU.
+    with NumaLocal(device.index) as numa:
+        host_a = a0.pin_memory()
+        host_bt = bt0.pin_memory()
+        host_outs = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     lanes = [sets[0], sets[1]]
     s_in, s_mm, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(2)]
@@ -414,6 +572,22 @@ def main() -> None:
     barrier(world)
     e2e_ms = max_over_ranks(e2e_run(e2e_steps), world)
     barrier(world)
+    # The copy legs alone, all ranks at once (they share the host's PCIe root and memory): what the
+    # end-to-end step is bounded by when it is slower than one GPU alone.
+    dev_a, dev_bt, dev_out = lanes[0]
+
+    def h2d(i):
+        dev_a.copy_(host_a, non_blocking=True)
+        dev_bt.copy_(host_bt, non_blocking=True)
+
+    def d2h(i):
+        host_outs[0].copy_(dev_out, non_blocking=True)
+
+    barrier(world)
+    h2d_ms = max_over_ranks(cuda_time_ms(h2d, 10), world)
+    barrier(world)
+    d2h_ms = max_over_ranks(cuda_time_ms(d2h, 10), world)
+    barrier(world)
     if rank == 0 and not torch.equal(host_outs[0], sets[0][2].cpu()):
         raise SystemExit("end-to-end result differs from the device-resident result")
 
@@ -427,47 +601,42 @@ def main() -> None:
 
     value = world * FLOPS / ms / 1e9
     achieved = FLOPS / ms / 1e9
-    # Denominator: the timed region is a long back-to-back loop, so when the clock record shows
-    # it ran under the power cap the sustained cuBLAS figure is the matching peak; a short run
-    # that was never capped is compared with the burst figure.
-    capped = "sw_power_cap" in (clocks or {}).get("reasons", []) and peaks["bf16_sustained"] > 0
-    peak = peaks["bf16_sustained"] if capped else peaks["bf16"]
-    peak_kind = "sustained (timed loop ran under sw_power_cap)" if capped else "burst"
+    # Denominator: the burst cuBLAS figure, unless the timed region itself lasts a second or more
+    # (then the seconds-long sustained figure is the matching one).  Both fractions are printed.
+    long_region = ms * args.steps >= 1000.0 and peaks["bf16_sustained"] > 0
+    peak = peaks["bf16_sustained"] if long_region else peaks["bf16"]
+    peak_kind = "sustained (timed region >= 1 s)" if long_region else "burst (timed region < 1 s)"
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "schedule": cfg.to_dict(), "schedule_choice": schedule_choice,
-                   "untimed_launches_before_the_timed_region": "warmup + schedule trials + 3000 while the clock sampler starts",
+                   "untimed_launches_before_the_timed_region": "warmup + 3000 while the clock sampler starts",
                    "l2": f"launches rotate over {len(sets)} operand sets, {len(sets) * ALGO_BYTES / 1e6:.0f} MB > 126 MB L2",
                    "parallelism": "replicas" if world > 1 else "1 GPU",
                    "inputs": "a, bt ~ N(0,1) from seed 0 (set 0); fp32 accumulate, bf16 out"},
         "clocks": clocks,
         "e2e": {"value": world * FLOPS / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(2 * (M * K + N * K)), "d2h_bytes_per_step": int(2 * M * N),
+                "h2d_gbs_per_gpu_alone_leg": 2.0 * (M * K + N * K) / h2d_ms / 1e6,
+                "d2h_gbs_per_gpu_alone_leg": 2.0 * M * N / d2h_ms / 1e6,
+                "copy_bound_ms_per_step": max(h2d_ms, d2h_ms), "host_buffers_numa": numa.info,
                 "api": "gemm_op('mm','bfloat16')(a, bt, out); every step copies a and bt in from pinned host memory and out back, three streams, two buffer sets; wall clock around the loop with a device synchronise on both sides"},
         "gpu_launches": args.steps,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
                      "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind}", "algorithmic_bytes": ALGO_BYTES,
-                     "frac_of_burst_peak": achieved / peaks["bf16"], "frac_of_nominal_2250": achieved / 2250.0},
+                     "frac_of_burst_peak": achieved / peaks["bf16"],
+                     "frac_of_sustained_peak": (achieved / peaks["bf16_sustained"]) if peaks["bf16_sustained"] else None,
+                     "frac_of_nominal_2250": achieved / 2250.0},
         "parity": {"fro_rel": parity.fro_rel, "max_over_rms": parity.max_over_rms,
                    "over_bound": parity.over_bound, "over_bound_one_ulp": parity.over_bound_one_ulp},
     }
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(a0, bt0)
         if not args.no_extra:
-            a, bt, out = sets[1]
-
-            def cublas(i):
-                a, bt, out = sets[i % len(sets)]
-                torch.mm(a, bt.t(), out=out)
-
-            for i in range(3):
-                cublas(i)
-            ms_t = cuda_time_ms(cublas, args.steps)
-            line["extra"] = {"torch_mm_tflops": FLOPS / ms_t / 1e9, "torch_mm_ms": ms_t,
-                             "swiglu": swiglu_extra(peaks)}
+            line["vs_cublas"] = vs_cublas
+            line["extra"] = {"swiglu": swiglu_extra(peaks), "hbm": hbm_rows(peaks)}
     else:
         line["sharded"] = sharded_results(args, rank, world, device)
         import torch.distributed as dist

@@ -181,9 +181,13 @@ AYLA_B200_API int ayla_b200_gemm_act_rowmul(int op, int dtype, int activation, c
  * AYLA_B200_E_WORKSPACE and a message naming both sizes (schedules with
  * split_k == 1 need none and always fit).
  *
- * The first call on a device that needs scratch resolves the array's device
- * address (a one-off runtime query); make that first call outside stream
- * capture.  All calls on a GPU share the one array and it keeps the previous
+ * There is no activation, gate or SwiGLU form of this entry point: it covers
+ * mm, addmm and bmm as ayla_b200_gemm does, nothing fused after them.
+ *
+ * The array's device address is resolved once per device (a runtime query made
+ * with that device current): by ayla_b200_init, and again lazily by the first
+ * call on a device that needs scratch should init not have done it; make that
+ * first call outside stream capture.  All calls on a GPU share the one array and it keeps the previous
  * call's contents: the entry point clears the arrival counters on `stream`
  * before each launch, and two calls whose kernels can overlap on the GPU
  * (different streams, no dependency) race on it -- serialise them.

@@ -164,3 +164,82 @@ def test_row_factor_op_is_registered_with_one_more_operand():
     assert op(a, bt, torch.empty(8, 1, dtype=torch.bfloat16, device="meta"), out) is None
     with pytest.raises(ValueError, match="unsupported gate"):
         gemm_jit_compiler("mm", "bfloat16", "none", gated="column")
+
+
+def test_launcher_makes_its_own_device_current_for_the_launch(monkeypatch):
+    """The library launches on the current device, so a launcher specialised for cuda:1 must switch
+    to it while cuda:0 is current (the reference's launcher guards the device the same way).
+    Driven with fakes: no GPU, no library call."""
+    import types
+
+    from ayla_b200.gemm_jit import GemmLauncher
+
+    current = [0]
+    launches = []
+
+    class FakeGuard:
+        def __init__(self, index):
+            self.index = index
+
+        def __enter__(self):
+            self.previous, current[0] = current[0], self.index
+
+        def __exit__(self, *exc):
+            current[0] = self.previous
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: current[0])
+    monkeypatch.setattr(torch.cuda, "device", FakeGuard)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda index=None: types.SimpleNamespace(cuda_stream=index))
+
+    launcher = object.__new__(GemmLauncher)
+    launcher.status = types.SimpleNamespace(peek=lambda: 0)
+    launcher._has_bias, launcher.gated, launcher._debug = False, False, False
+    launcher._head, launcher._tail, launcher._device_index = (0, 1, 0), (), 1
+    launcher._entry = lambda *args: launches.append((current[0], args[-1])) or 0
+    tensor = types.SimpleNamespace(data_ptr=lambda: 16)
+    launcher(tensor, tensor, tensor)
+    assert launches == [(1, 1)]      # launched with cuda:1 current, on cuda:1's stream
+    assert current[0] == 0           # and the caller's device is current again
+    launcher._device_index = 0
+    launcher(tensor, tensor, tensor)
+    assert launches[-1] == (0, 0)
+
+
+def test_launcher_reports_a_timed_out_launch_before_the_next_one(monkeypatch):
+    """A non-zero status word (left by an earlier launch whose bounded wait gave up) makes the next
+    call raise instead of launching, clears the word, and the call after that launches again."""
+    import types
+
+    from ayla_b200.gemm_jit import GemmLauncher
+
+    word = [0x203]  # code 3 from CTA 2
+    cleared = []
+    launcher = object.__new__(GemmLauncher)
+    launcher.status = types.SimpleNamespace(peek=lambda: word[0], clear=lambda: word.__setitem__(0, 0))
+    launcher.workspace = types.SimpleNamespace(zero_=lambda: cleared.append("workspace"))
+    launcher.operation = "mm"
+    launcher._has_bias, launcher.gated, launcher._debug = False, False, False
+    launcher._head, launcher._tail, launcher._device_index = (0, 1, 0), (), 0
+    launches = []
+    launcher._entry = lambda *args: launches.append(args) or 0
+
+    class NoGuard:
+        def __init__(self, index):
+            pass
+
+        def __enter__(self):
+            pass
+
+        def __exit__(self, *exc):
+            pass
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    monkeypatch.setattr(torch.cuda, "device", NoGuard)
+    monkeypatch.setattr(torch.cuda, "current_stream",
+                        lambda index=None: types.SimpleNamespace(cuda_stream=0, synchronize=lambda: None))
+    tensor = types.SimpleNamespace(data_ptr=lambda: 16)
+    with pytest.raises(RuntimeError, match=r"timed out \(code 3, CTA 2\)"):
+        launcher(tensor, tensor, tensor)
+    assert launches == [] and cleared == ["workspace"] and word[0] == 0
+    launcher(tensor, tensor, tensor)
+    assert len(launches) == 1

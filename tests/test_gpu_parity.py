@@ -675,6 +675,47 @@ def test_launcher_check_status_raises_on_timeout():
     torch.testing.assert_close(out, a @ a.T, atol=0.125, rtol=0.02)
 
 
+def test_timed_out_split_k_launch_is_reported_by_the_next_call_without_the_debug_switch(monkeypatch):
+    """The status word sits in pinned host memory and is read before every launch: after a k-split
+    launch that ran into a bounded wait, the next call of that shape raises (no AYLA_B200_DEBUG, no
+    explicit check_status), and the call after it is correct -- the arrival counters a timed-out
+    k-split may leave behind are cleared with the report."""
+    from ayla_b200.gemm_jit import GemmLauncher, GemmScheduleSeed, _DEFAULTS
+
+    monkeypatch.delenv("AYLA_B200_DEBUG", raising=False)
+    lib = _lib.load()
+    m, n, k = 256, 256, 2048
+    captured = {**_DEFAULTS, "tile_n": 64, "cta_group": 1, "split_k": 4}
+    seed = GemmScheduleSeed(captured, {key: int(captured[key]) for key in _lib.Config.FIELDS}, (), (m, n, k))
+    launcher = GemmLauncher("mm", "bfloat16", 1, m, n, k, seed, torch.device(DEV))
+    assert launcher.workspace is not None and not launcher._debug
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    bt = (torch.randn(n, k, generator=g) * k ** -0.5).bfloat16()
+    da, dbt = a.to(DEV), bt.to(DEV)
+    out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    launcher(da, dbt, out)
+    torch.cuda.synchronize()
+    assert launcher.status.peek() == 0
+    assert_parity(out, O.mm_ref32(a, bt), "k-split launch before the failure")
+    try:
+        lib.ayla_b200_set_wait_timeout_ms(30)
+        lib.ayla_b200_debug_set_flags(1)
+        launcher(da, dbt, out)          # the producer delivers nothing: the waits run out
+        torch.cuda.synchronize()
+    finally:
+        lib.ayla_b200_debug_set_flags(0)
+        lib.ayla_b200_set_wait_timeout_ms(2000)
+    assert launcher.status.peek() & 0xFF in (2, 4)
+    with pytest.raises(RuntimeError, match="timed out"):
+        launcher(da, dbt, out)
+    out.zero_()
+    launcher(da, dbt, out)
+    torch.cuda.synchronize()
+    assert launcher.status.peek() == 0
+    assert_parity(out, O.mm_ref32(a, bt), "k-split launch after a reported timeout")
+
+
 def test_random_shapes_through_the_public_ops():
     """Schedule selection on shapes nobody measured: transferred table entries (trimmed tiles, 192-wide
     tiles, cluster k-splits, eviction hints) and the default heuristic must all stay correct on ragged

@@ -36,6 +36,32 @@ def test_c_restatement_agrees_with_golden_up_to_rounding_flips(case):
     assert parity.ok
 
 
+@pytest.mark.parametrize("operation, dtype, m, n, k, a_scale, b_scale", [
+    ("mm", torch.bfloat16, 64, 256, 4096, 1.0, 4096 ** -0.5),      # a long accumulation, sweep-like operands
+    ("addmm", torch.float16, 32, 128, 16384, 1.0, 16384 ** -0.5),  # the split-K config's depth, scaled down in M and N
+    ("mm", torch.bfloat16, 48, 64, 8192, 1.0, 1.0),                # unscaled operands: results far from 1
+])
+def test_deep_k_torch_oracle_against_the_independent_c_restatement(operation, dtype, m, n, k, a_scale, b_scale):
+    """Something that is not torch checks torch on long accumulations: the fp64 plain-C
+    restatement and the fp32 torch oracle may differ only by flips of the final rounding
+    (one output ulp), and the C result must satisfy the project's tolerance against torch's."""
+    g = torch.Generator().manual_seed(k + m)
+    a = (torch.randn(m, k, generator=g) * a_scale).to(dtype)
+    bt = (torch.randn(n, k, generator=g) * b_scale).to(dtype)
+    bias = (torch.randn(n, generator=g) * 0.1).to(dtype)
+    operands = (bias, a, bt) if operation == "addmm" else (a, bt)
+    want32 = O.addmm_ref32(*operands) if operation == "addmm" else O.mm_ref32(*operands)
+    want = want32.to(dtype)
+    got = gemm_c(operation, *operands)
+    parity = O.compare(got, want32)
+    assert parity.ok and parity.nonfinite == 0, parity
+    differing = int((got.view(torch.int16) != want.view(torch.int16)).sum())
+    assert differing <= max(2, got.numel() // 100), differing
+    rms = float(want32.pow(2).mean().sqrt())
+    ulp = O._ulp(want32.abs().clamp_min(1e-2 * rms), dtype)
+    assert bool(((got.float() - want.float()).abs() <= ulp * 1.0001).all())
+
+
 def test_c_restatement_known_answers():
     """Identity and one-hot operands give exactly representable results."""
     for dtype in (torch.bfloat16, torch.float16):

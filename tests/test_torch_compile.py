@@ -172,6 +172,61 @@ def test_swiglu_on_a_concatenated_weight_is_fused():
     assert tc.route_swiglu_concat(gm.graph) == 0
 
 
+def test_swiglu_on_a_concatenated_weight_spelled_as_two_slices_is_fused():
+    """The form a captured decoder block holds (the reference's
+    benchmarks/bench_torch_compile/corpus/muse_glimmer_block.py:42-50): the gate half is
+    ``slice(mm, 1, 0, n)``, the up half ``slice(mm, 1, n, INT64_MAX)``, silu decomposed in fp32."""
+    big = 9223372036854775807
+
+    def block(x, w_t):
+        mm = aten.mm.default(x, w_t)
+        gate = aten.slice.Tensor(mm, 1, 0, 48)
+        g32 = torch.ops.prims.convert_element_type.default(gate, torch.float32)
+        act = torch.ops.prims.convert_element_type.default(
+            aten.div.Tensor(g32, aten.add.Tensor(aten.exp.default(aten.neg.default(g32)), 1)), torch.bfloat16)
+        up = aten.slice.Tensor(mm, 1, 48, big)
+        return aten.mul.Tensor(act, up)
+
+    def traced(x, w):
+        return block(x, w.t())
+
+    gm = trace(traced, ((64, 32), BF16, "cuda"), ((96, 32), BF16, "cuda"))
+    assert aten.slice.Tensor in targets(gm)
+    assert tc.route_swiglu_concat(gm.graph) == 1
+    gm.graph.lint()
+    assert torch.ops.ayla.swiglu_bf16_fn.default in targets(gm) and aten.mm.default not in targets(gm)
+
+    # slices that are not the two halves are left alone
+    def uneven(x, w):
+        mm = aten.mm.default(x, w.t())
+        return torch.nn.functional.silu(aten.slice.Tensor(mm, 1, 0, 32)) * aten.slice.Tensor(mm, 1, 64, big)
+
+    gm = trace(uneven, ((64, 32), BF16, "cuda"), ((96, 32), BF16, "cuda"))
+    assert tc.route_swiglu_concat(gm.graph) == 0
+
+
+def test_every_op_the_pass_can_emit_is_registered_by_install():
+    """On a hit in Inductor's code cache the pass never runs in the new process: the cached code
+    names torch.ops.ayla.* ops, which must exist after install() alone."""
+    from ayla_b200.gemm_jit import ACTIVATIONS, _op_name
+
+    previous = inductor_config.post_grad_custom_post_pass
+    try:
+        tc.install()
+        for dtype, short in (("float16", "f16"), ("bfloat16", "bf16")):
+            assert hasattr(torch.ops.ayla, f"swiglu_{short}_fn")
+            for operation in ("mm", "addmm", "bmm"):
+                for activation in ACTIVATIONS:
+                    for gated in (False, True):
+                        name = f"{_op_name(operation, dtype, activation, gated)}_fn"
+                        assert hasattr(torch.ops.ayla, name), name
+        # every activation the matcher can name is one of those
+        assert {"relu", "sigmoid", "silu", "gelu", "gelu_tanh"} <= set(ACTIVATIONS)
+    finally:
+        tc.uninstall()
+        inductor_config.post_grad_custom_post_pass = previous
+
+
 def test_install_is_idempotent_and_uninstall_restores():
     previous = inductor_config.post_grad_custom_post_pass
     try:

@@ -42,9 +42,11 @@ def _both(op, dtype, tensors, cfg_dict, repeats=2):
     assert int(status.item()) == 0 and not torch.isnan(want).any()
     for _ in range(repeats):
         got = torch.full_like(want, float("nan"))
+        free_before = torch.cuda.mem_get_info()[0]
         _lib.gemm_static_scratch(op, dtype, bias.data_ptr() if bias is not None else 0, a.data_ptr(),
                                  bt.data_ptr(), got.data_ptr(), batch, m, n, k, cfg, status.data_ptr(), stream)
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         assert int(status.item()) == 0
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
