@@ -59,6 +59,7 @@ class Config(ctypes.Structure):
         ("cluster_split", ctypes.c_int32),
         ("stream_k", ctypes.c_int32),
         ("tile_rows", ctypes.c_int32),
+        ("early_prefetch", ctypes.c_int32),
     ]
 
     FIELDS = tuple(name for name, _ in _fields_)
@@ -66,7 +67,8 @@ class Config(ctypes.Structure):
     @classmethod
     def from_dict(cls, values: dict) -> "Config":
         cfg = cls(tile_n=256, cta_group=1, swap_ab=0, split_k=1, group_m=8, grid_ctas=0,
-                  l2_hint_a=0, l2_hint_b=0, split_tail=0, l2_prefetch=0, cluster_split=0, stream_k=0, tile_rows=0)
+                  l2_hint_a=0, l2_hint_b=0, split_tail=0, l2_prefetch=0, cluster_split=0, stream_k=0, tile_rows=0,
+                  early_prefetch=0)
         for key in cls.FIELDS:
             if key in values and values[key] is not None:
                 setattr(cfg, key, int(values[key]))

@@ -233,6 +233,9 @@ int check_config(const ayla_b200_config& c, bool swiglu) {
   if (c.l2_prefetch < 0 || c.l2_prefetch > 256) {
     return fail(AYLA_B200_E_UNSUPPORTED, "l2_prefetch must be between 0 and 256 k-blocks");
   }
+  if (c.early_prefetch < 0 || c.early_prefetch > 32) {
+    return fail(AYLA_B200_E_UNSUPPORTED, "early_prefetch must be between 0 and 32 k-blocks");
+  }
   if (c.stream_k != 0 && c.stream_k != 1) {
     return fail(AYLA_B200_E_UNSUPPORTED, "stream_k must be 0 or 1");
   }
@@ -470,6 +473,11 @@ void default_config(int64_t batch, int64_t m, int64_t n, int64_t k, int sm_count
       }
     }
     c->group_m = 1;
+    // Weight streaming is what early_prefetch is for: half of the CTA's share of K, 16 k-blocks at most.
+    {
+      const int64_t share = k_blocks / c->split_k / 2;
+      c->early_prefetch = static_cast<int>(share < 16 ? share : 16);
+    }
     if (c->split_k == 1 && m > 16) {
       // No room to split K (bt alone fills the SMs): with a few dozen rows of `a` the plain
       // row-major 128-wide tile, its `a` box trimmed to the rows that exist, measures 1.2-1.3x
@@ -606,6 +614,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.timeout_ns = static_cast<unsigned long long>(g_timeout_ns.load());
   p.debug_flags = g_debug_flags.load();
   p.l2_prefetch = c.l2_prefetch;
+  p.early_prefetch = c.early_prefetch;
   p.tile_rows = plan.tile_rows;
   p.act = activation;
   p.mul = mul;

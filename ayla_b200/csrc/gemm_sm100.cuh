@@ -77,6 +77,7 @@ struct KernelParams {
   long long* trace;   // per-CTA cycle counters, written only by AYLA_B200_TRACE builds
   int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
   int l2_prefetch;    // k-blocks the producer prefetches into L2 ahead of its shared-memory loads
+  int early_prefetch; // k-blocks of the CTA's first unit asked into L2 before the dependency wait
   const void* mul;    // optional gate, same shape and layout as `out`: out = act(...) * mul (activation variants)
   int mul_per_row;    // non-zero: `mul` holds one element per output row instead ([batch][rows])
   int act;            // activation applied to the fp32 result (after the bias) before rounding: ACT_*
@@ -437,7 +438,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // landed, last MMA committed, epilogue done, exit.
   // Slots: 0 entry, 1 set-up done, 2 first operands landed, 3 last MMA committed, 4 epilogue done, 5 exit,
   // 6/7 cluster split-K barriers, 8 SM id, 9-11 a quarter / half / three quarters of the CTA's first unit
-  // issued, 12 first TMA load issued, 13 epilogue saw the first finished accumulator.
+  // issued, 12 first TMA load issued, 13 epilogue saw the first finished accumulator, 14 the preceding
+  // launch is complete (dependency wait returned).
   long long* stamps = (p.trace != nullptr) ? p.trace + 4096 + blockIdx.x * 16 : nullptr;
   if (stamps != nullptr && threadIdx.x == 0) {
     stamps[0] = static_cast<long long>(global_timer_ns());
@@ -504,11 +506,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (stamps != nullptr && threadIdx.x == 32) stamps[1] = static_cast<long long>(global_timer_ns());
 #endif
 
-  // Everything above touched only this launch's own shared memory, TMEM and parameters.
-  // From here on global memory is read and written, so the launch that precedes this one
-  // in the stream must be complete (a no-op unless the launch was allowed to start early);
-  // after that the next launch may begin its own set-up on SMs that fall idle.
-  grid_dependency_wait();
+  // Everything above touched only this launch's own shared memory, TMEM and parameters, and so
+  // does each role's own preparation below (schedule arithmetic, cache policies, L2 prefetches,
+  // which move no data into this kernel).  A role executes griddepcontrol.wait itself right
+  // before its first read or write of global memory: the launch that precedes this one in the
+  // stream is then complete (a no-op unless the launch was allowed to start early).  The next
+  // launch may begin its own set-up on SMs that fall idle from here on.
   grid_launch_dependents();
 
   // Cluster split-K: the cluster holds `csk` CTAs (CTA pairs when CG == 2), one per k-split
@@ -533,9 +536,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full_bar0 = (CG == 2) ? map_to_cta(bar_full, pair_base) : bar_full;
     uint32_t stage = 0, phase = 0;
+#ifdef AYLA_B200_TRACE
+    bool first_issue_stamped = false;
+#endif
     AYLA_TRACE_BEGIN
     UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank, csk_rank);
     WorkUnit w;
+    bool dependency_met = false;
     while (cursor.next(w)) {
       if (bw.aborted()) break;
       // A narrow unit needs only the first half of each CTA's B slab; the full box is
@@ -552,6 +559,20 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if constexpr (T::EPI == EPI_SWIGLU && CG == 1) tma_prefetch_l2_3d(&tm_b2, kb * T::BK, b_row, 0);
       };
       const int pf = p.l2_prefetch;
+      if (!dependency_met) {
+        // Before the preceding launch is known to be complete nothing may be read into this
+        // kernel, but its first operands may be asked into L2 (a prefetch delivers no data, and
+        // L2 stays coherent with whatever that launch still writes): the loads issued after the
+        // wait then find them there instead of paying the DRAM latency with an empty ring.
+        if (issuer) {
+          for (int kb = w.kb0; kb < w.kb1 && kb < w.kb0 + p.early_prefetch; ++kb) prefetch_l2(kb);
+        }
+        grid_dependency_wait();
+        dependency_met = true;
+#ifdef AYLA_B200_TRACE
+        if (stamps != nullptr && lane == 0) stamps[14] = static_cast<long long>(global_timer_ns());
+#endif
+      }
       if (issuer && pf > 0) {
         for (int kb = w.kb0; kb < w.kb1 && kb < w.kb0 + pf; ++kb) prefetch_l2(kb);
       }
@@ -559,7 +580,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
         if (issuer) {
 #ifdef AYLA_B200_TRACE
-          if (stamps != nullptr && stamps[12] == 0) stamps[12] = static_cast<long long>(global_timer_ns());
+          if (stamps != nullptr && !first_issue_stamped) {
+            stamps[12] = static_cast<long long>(global_timer_ns());
+            first_issue_stamped = true;
+          }
 #endif
           const uint32_t full_bar = full_bar0 + stage * 8;
           if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, p.stage_tx);
@@ -602,6 +626,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t acc = 0, acc_phase = 0;
 #ifdef AYLA_B200_TRACE
       bool first_operands_stamped = false;
+      bool first_unit_of_cta = true;
 #endif
       AYLA_TRACE_BEGIN
       UnitCursor<T> cursor(p, first_unit, unit_stride, 0, csk_rank);
@@ -612,19 +637,18 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         const uint32_t unit_idesc = w.is_narrow ? p.idesc_narrow : idesc;
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        const int nkb = w.kb1 - w.kb0;
+        for (int i = 0; i < nkb; ++i) {
           AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL))
 #ifdef AYLA_B200_TRACE
           if (stamps != nullptr && lane == 0 && !first_operands_stamped) {
             stamps[2] = static_cast<long long>(global_timer_ns());
             first_operands_stamped = true;
           }
-          if (stamps != nullptr && lane == 0 && stamps[3] == 0) {
-            const int span = w.kb1 - w.kb0, done = kb - w.kb0;
+          if (stamps != nullptr && lane == 0 && first_unit_of_cta) {
+            const int span = nkb, done = i;
             for (int qd = 1; qd <= 3; ++qd) {
-              if (span >= 4 && done == qd * span / 4 && stamps[8 + qd] == 0) {
-                stamps[8 + qd] = static_cast<long long>(global_timer_ns());
-              }
+              if (span >= 4 && done == qd * span / 4) stamps[8 + qd] = static_cast<long long>(global_timer_ns());
             }
           }
 #endif
@@ -636,14 +660,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
             for (int k4 = 0; k4 < T::BK / 16; ++k4) {
               umma_f16<CG>(tmem_d, desc_a0 + (stage_off + 2 * k4), desc_b0 + (stage_off + 2 * k4), unit_idesc,
-                           (kb > w.kb0 || k4 > 0) ? 1u : 0u);
+                           (i > 0 || k4 > 0) ? 1u : 0u);
             }
             if constexpr (CG == 1) {
               umma_commit_1cta(bar_empty + stage * 8);
             } else {
               umma_commit_2cta(bar_empty + stage * 8, pair_mask);
             }
-            if (kb == w.kb1 - 1) {
+            if (i == nkb - 1) {
               if constexpr (CG == 1) {
                 umma_commit_1cta(bar_acc_full + acc * 8);
               } else {
@@ -660,6 +684,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           acc = 0;
           acc_phase ^= 1;
         }
+#ifdef AYLA_B200_TRACE
+        first_unit_of_cta = false;
+#endif
       }
       AYLA_TRACE_END(1)
 #ifdef AYLA_B200_TRACE
@@ -692,6 +719,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     constexpr int EPI_THREADS = T::EPI_WARPS * 32;
     const uint32_t acc_empty_leader =
         (CG == 2) ? map_to_cta(bar_acc_empty, pair_base) : bar_acc_empty;
+#ifdef AYLA_B200_TRACE
+    bool acc_seen_stamped = false;
+#endif
     AYLA_TRACE_BEGIN
 
     // No early exit in this loop: the warps meet at named barriers, so after an abort
@@ -699,6 +729,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // results are garbage that the status word disowns.
     UnitCursor<T> cursor(p, first_unit, unit_stride, cta_rank, csk_rank);
     WorkUnit w;
+    grid_dependency_wait();  // these warps read bias / gate operands and write the output
     while (cursor.next(w)) {
       const bool split_k = T::LEAN ? false : w.is_split;
 
@@ -715,7 +746,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
       AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL))
 #ifdef AYLA_B200_TRACE
-      if (stamps != nullptr && warp == 2 && lane == 0 && stamps[13] == 0) stamps[13] = static_cast<long long>(global_timer_ns());
+      if (stamps != nullptr && warp == 2 && lane == 0 && !acc_seen_stamped) {
+        stamps[13] = static_cast<long long>(global_timer_ns());
+        acc_seen_stamped = true;
+      }
 #endif
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;

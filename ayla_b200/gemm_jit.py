@@ -50,6 +50,7 @@ _DEFAULTS: dict[str, object] = {
     "cluster_split": 0,
     "stream_k": 0,
     "tile_rows": 0,
+    "early_prefetch": 0,
 }
 
 # A measured schedule is transferred to another shape only when the shapes are

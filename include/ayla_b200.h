@@ -80,6 +80,13 @@ typedef struct ayla_b200_config {
                          128 rows; fewer rows per tile means more, lighter tiles, so that a
                          weight whose 128-row tiles would leave SMs idle (112 tiles for
                          n = 14336 on 148 SMs) is streamed by all of them. */
+  int32_t early_prefetch; /* k-blocks (0..32) of a CTA's first tile that its producer asks into L2 before
+                             the kernel waits for the preceding launch in the stream (launch overlap on).
+                             A prefetch delivers nothing into the kernel and L2 stays coherent with
+                             whatever that launch still writes, so this is safe whatever it produces;
+                             it fills the DRAM time the preceding launch's tail leaves idle.  Pays for
+                             weight-streaming (small M) launches issued back to back, costs a little
+                             where the operands are L2-resident anyway. */
 } ayla_b200_config;
 
 /*
