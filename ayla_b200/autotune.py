@@ -162,6 +162,11 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
     times = time_interleaved(fns, launches, rounds)
     torch_ms = times.pop("torch")
     ranked = sorted(times.items(), key=lambda kv: kv[1])
+    if not ranked:
+        del sets
+        torch.cuda.empty_cache()
+        return dict(op=op, dtype=dtype, batch=batch, m=m, n=n, k=k, torch_us=torch_ms * 1e3, results=[])
+
     def refine_pass(tweaks_for, label):
         """Time variations of the two fastest schedules next to the fastest itself (the yardstick that
         ties this pass's times to the first pass's) and merge them into the ranking."""
