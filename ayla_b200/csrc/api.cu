@@ -615,6 +615,46 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   p.debug_flags = g_debug_flags.load();
   p.l2_prefetch = c.l2_prefetch;
   p.early_prefetch = c.early_prefetch;
+  // The early prefetch covers the operand that carries the bytes (a weight against a few rows of
+  // activations); both when they are within a factor of four of each other.
+  p.early_operands = (pr.rows * 4 >= pr.cols ? 1 : 0) | (pr.cols * 4 >= pr.rows ? 2 : 0);
+  p.div_tiles_per_batch = FastDiv::make(static_cast<uint32_t>(plan.m_tiles) * static_cast<uint32_t>(plan.n_tiles));
+  p.div_group_size = FastDiv::make(static_cast<uint32_t>(plan.group_m) * static_cast<uint32_t>(plan.n_tiles));
+  p.div_group_m = FastDiv::make(static_cast<uint32_t>(plan.group_m));
+  p.div_last_group_rows = FastDiv::make(static_cast<uint32_t>(plan.m_tiles % plan.group_m));
+  p.div_splits = FastDiv::make(static_cast<uint32_t>(plan.splits));
+  {
+    int per_unit = e.cta_group * (plan.cluster_split > 0 ? plan.cluster_split : 1), log2 = 0;
+    while ((1 << log2) < per_unit) ++log2;
+    p.ctas_per_unit_log2 = log2;
+  }
+  p.stages = e.stages;
+  if (plan.cluster_split > 0) {
+    // Cluster split-K: every CTA receives the other k-splits' partials of the columns it owns in an
+    // inbox of shared memory.  The inbox takes the top of the ring region; the ring gives up the
+    // slots it covers as long as three remain, otherwise the inbox overlays live slots and the
+    // kernel holds the partials back until the whole cluster is done with its MMAs.
+    const int csk = plan.cluster_split;
+    const int slice_cols = e.tile_n / csk;
+    const int chunk_cols = e.tile_n < 32 ? e.tile_n : 32;
+    const int slots = (slice_cols >= chunk_cols) ? csk - 1 : csk;
+    const int inbox_bytes = slots * 128 * slice_cols * 4;
+    const int stage_bytes = e.kb_per_slot * (128 * 64 * 2 + (e.tile_n / e.cta_group) * 64 * 2);  // one ring slot
+    const int ring_bytes = e.stages * stage_bytes;
+    if (inbox_bytes > ring_bytes) {
+      return fail(AYLA_B200_E_UNSUPPORTED, "cluster_split: the %d-byte inbox does not fit the %d-byte ring", inbox_bytes,
+                  ring_bytes);
+    }
+    const int free_stages = (ring_bytes - inbox_bytes) / stage_bytes;
+    p.inbox_tx = static_cast<uint32_t>(inbox_bytes);
+    p.inbox_offset = static_cast<uint32_t>(ring_bytes - inbox_bytes);
+    if (free_stages >= 3 && (g_debug_flags.load() & 2) == 0) {
+      p.stages = free_stages;
+      p.inbox_in_ring = 0;
+    } else {
+      p.inbox_in_ring = 1;
+    }
+  }
   p.tile_rows = plan.tile_rows;
   p.act = activation;
   p.mul = mul;

@@ -6,8 +6,9 @@
 // (ayla/gemm_jit.py:267-307): fp16/bf16 inputs, fp32 accumulation, one rounding
 // to the output type at the end (ayla/passes/lower_to_ptx_template.py:134-149).
 //
-// One CTA = 10 warps:
-//   warp 0      TMA producer  : global -> shared ring of STAGES (A 128x64, B BNx64) slabs
+// One CTA = 11 warps:
+//   warps 0, 10 TMA producers : global -> shared ring of STAGES (A 128x64, B BNx64) slabs, every
+//                               other k-block each (one thread cannot start TMA loads fast enough)
 //   warp 1      MMA issuer    : tcgen05.mma from shared into a TMEM accumulator;
 //                               also owns the TMEM allocation
 //   warps 2..9  epilogue      : TMEM -> registers -> (bias | activation | SiLU*up) -> round ->
@@ -43,6 +44,30 @@ enum : unsigned {
   ST_TIMEOUT_ACC_EMPTY = 3,  // MMA warp waited for a drained accumulator
   ST_TIMEOUT_ACC_FULL = 4,   // epilogue waited for a finished accumulator
   ST_BAD_SMEM_ALIGN = 5,
+  ST_TIMEOUT_INBOX = 6,      // epilogue waited for the other k-splits' partial sums (cluster split-K)
+};
+
+// Division of a non-negative 32-bit value by a divisor fixed at launch: q = (n * mul) >> (32 + shift),
+// with mul and shift worked out on the host (exact for n < 2^31).  A plain `/` on run-time values
+// costs a dependent chain of some twenty instructions, and the schedule arithmetic at the head of
+// every role has half a dozen of them in front of the first load.
+struct FastDiv {
+  uint32_t mul;    // 0: the divisor is 1
+  uint32_t shift;
+  __host__ __device__ static FastDiv make(uint32_t d) {
+    FastDiv f{0u, 0u};
+    if (d <= 1) return f;
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;                       // ceil(log2 d) >= 1
+    f.mul = static_cast<uint32_t>(((1ull << (31 + l)) / d) + 1);
+    f.shift = l - 1;
+    return f;
+  }
+#ifdef __CUDACC__
+  __device__ __forceinline__ int div(int n) const {
+    return mul == 0 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shift);
+  }
+#endif
 };
 
 struct KernelParams {
@@ -78,6 +103,19 @@ struct KernelParams {
   int debug_flags;    // bit 0: the producer issues no loads (exercises the bounded waits)
   int l2_prefetch;    // k-blocks the producer prefetches into L2 ahead of its shared-memory loads
   int early_prefetch; // k-blocks of the CTA's first unit asked into L2 before the dependency wait
+  int early_operands; // which operands that prefetch covers: bit 0 the row operand, bit 1 the column operand
+  FastDiv div_tiles_per_batch;  // by m_tiles * n_tiles
+  FastDiv div_group_size;       // by group_m * n_tiles
+  FastDiv div_group_m;          // by group_m
+  FastDiv div_last_group_rows;  // by the row tiles of the last, partial raster group (m_tiles % group_m)
+  FastDiv div_splits;           // by splits
+  int ctas_per_unit_log2;       // log2(CTA_GROUP * cluster_split or 1)
+  int stages;         // ring slots in use (<= the kernel's STAGES); fewer when the top of the ring region
+                      // is set aside as the inbox of a cluster split-K launch
+  uint32_t inbox_offset;  // cluster split-K: byte offset of the inbox from the start of shared memory
+  uint32_t inbox_tx;      // bytes the inbox receives per launch
+  int inbox_in_ring;      // 1: the inbox overlays ring slots that are in use, so partial sums may only be
+                          // sent once every CTA of the cluster has finished its MMAs (one cluster barrier)
   const void* mul;    // optional gate, same shape and layout as `out`: out = act(...) * mul (activation variants)
   int mul_per_row;    // non-zero: `mul` holds one element per output row instead ([batch][rows])
   int act;            // activation applied to the fp32 result (after the bias) before rounding: ACT_*
@@ -124,7 +162,14 @@ struct GemmTraits {
   static constexpr int B_ROWS = BN / CTA_GROUP; // B rows this CTA loads per stage
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = B_ROWS * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // one k-block of both operands
+  // Consecutive k-blocks per slot of the ring (one barrier pair for all of them).  Handing a slot
+  // from the loading warps to the MMA warp and back costs a few hundred cycles whatever the slot
+  // holds; the MMAs of one k-block of a tile narrower than 256 columns take less than that, so
+  // those tiles move two k-blocks per slot (measured on B200: M = 512, N = K = 4096 on 256 x 128
+  // pair tiles 20.7 -> 17.9 us; M = 8, N = 14336 21.5 -> 19.3 us; four per slot gained nothing more).
+  static constexpr int KB_PER_SLOT = (BN >= 256 || (BN == 192 && CTA_GROUP == 1)) ? 1 : 2;  // at least three slots
+  static constexpr int SLOT_BYTES = KB_PER_SLOT * STAGE_BYTES;
   static constexpr int ACC_BUFS = 2;
   static constexpr int TMEM_COLS_NEEDED = ACC_BUFS * BN;
   static constexpr int TMEM_COLS = TMEM_COLS_NEEDED <= 32    ? 32
@@ -137,14 +182,16 @@ struct GemmTraits {
   static constexpr int STORE_BYTES = TRANS_OUT ? 0 : EPI_WARPS * STORE_BUF_BYTES;
   static constexpr int BIAS_BYTES = (EPI == EPI_BIAS && !TRANS_OUT) ? 2 * BN * 4 : 0;
   static constexpr int MISC_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BIAS_BYTES + MISC_BYTES;
-  static constexpr int THREADS = 64 + EPI_WARPS * 32;
+  static constexpr int SMEM_BYTES = STAGES * SLOT_BYTES + STORE_BYTES + BIAS_BYTES + MISC_BYTES;
+  // Warps: 0 = first TMA producer, 1 = MMA issuer, 2..9 = epilogue, 10 = second TMA producer.
+  static constexpr int PRODUCER2_WARP = 2 + EPI_WARPS;
+  static constexpr int THREADS = 64 + EPI_WARPS * 32 + 32;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05 N extent");
   static_assert(B_BYTES % 1024 == 0, "B slab must keep the 1024-byte swizzle alignment");
   static_assert(EPI != EPI_SWIGLU || (BN == 256 && !TRANS_OUT), "SwiGLU uses the 2x128 layout");
   static_assert(TRANS_OUT || BN >= 64, "the TMA-store epilogue writes 64-column boxes");
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
-  static_assert((2 * STAGES + 2 * ACC_BUFS) * 8 + 16 <= MISC_BYTES, "barrier area too small");
+  static_assert((2 * STAGES + 2 * ACC_BUFS + 1) * 8 + 16 <= MISC_BYTES, "barrier area too small");
 };
 
 // A wait that gives up: polls the barrier, and every few thousand polls checks a
@@ -199,15 +246,16 @@ template <class T>
 __device__ __forceinline__ void locate_tile(const KernelParams& p, int tile, int half, int cta_rank,
                                             WorkUnit& w) {
   const int tiles_per_batch = p.m_tiles * p.n_tiles;
-  w.batch = tile / tiles_per_batch;
+  w.batch = p.div_tiles_per_batch.div(tile);
   const int t = tile - w.batch * tiles_per_batch;
   const int group_size = p.group_m * p.n_tiles;
-  const int g = t / group_size;
+  const int g = p.div_group_size.div(t);
   const int first_m = g * p.group_m;
-  const int rows_in_group = min(p.m_tiles - first_m, p.group_m);
+  const bool full_group = p.m_tiles - first_m >= p.group_m;
+  const int rows_in_group = full_group ? p.group_m : p.m_tiles - first_m;
   const int r = t - g * group_size;
-  const int m_t = first_m + r % rows_in_group;
-  const int n_t = r / rows_in_group;
+  const int n_t = full_group ? p.div_group_m.div(r) : p.div_last_group_rows.div(r);
+  const int m_t = first_m + (r - n_t * rows_in_group);
   // The swapped form may use fewer than 128 rows of its tile (tile_rows).
   w.m0 = T::TRANS_OUT ? m_t * p.tile_rows : (m_t * T::CTA_GROUP + cta_rank) * T::BM;
   w.n0 = n_t * T::OUT_BN + half * (T::OUT_BN / 2);
@@ -279,8 +327,9 @@ struct UnitCursor {
       tile = unit;
     } else {
       const int u = unit - p.split_from_tile;
-      tile = p.split_from_tile + u / p.splits;
-      w.split = u - (u / p.splits) * p.splits;
+      const int q = p.div_splits.div(u);
+      tile = p.split_from_tile + q;
+      w.split = u - q * p.splits;
       w.nsplit = p.splits;
       w.is_split = p.splits > 1;
     }
@@ -418,16 +467,17 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   constexpr int STAGES = T::STAGES;
 
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* smem_store = smem + STAGES * T::STAGE_BYTES;
+  uint8_t* smem_store = smem + STAGES * T::SLOT_BYTES;
   float* smem_bias = reinterpret_cast<float*>(smem_store + T::STORE_BYTES);
   uint8_t* smem_misc = smem_store + T::STORE_BYTES + T::BIAS_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_misc);
-  // barrier layout: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  // barrier layout: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], inbox
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + STAGES * 8;
   const uint32_t bar_acc_full = bar_empty + STAGES * 8;
   const uint32_t bar_acc_empty = bar_acc_full + T::ACC_BUFS * 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * T::ACC_BUFS);
+  const uint32_t bar_inbox = bar_acc_empty + T::ACC_BUFS * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * T::ACC_BUFS + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* last_flag = tmem_slot + 2;
 
@@ -458,6 +508,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const bool is_leader = cta_rank == 0;
 
   const BoundedWait bw{abort_flag, p.status, p.timeout_ns};
+  // Cluster split-K: the cluster holds `csk` CTAs (CTA pairs when CG == 2), one per k-split
+  // of the cluster's tile.
+  const int csk = (T::EPI != EPI_SWIGLU && !T::LEAN) ? p.cluster_split : 0;
+  constexpr int group = T::KB_PER_SLOT;  // k-blocks per ring slot
+  const int n_stages = p.stages;         // ring slots in use
 
   if (threadIdx.x == 0) {
     // Descriptor fetches first: they overlap the barrier set-up below.
@@ -476,6 +531,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       mbar_init(bar_acc_full + b * 8, 1);
       mbar_init(bar_acc_empty + b * 8, T::EPI_WARPS * CG);
     }
+    mbar_init(bar_inbox, 1);
+    // The inbox is used once per launch (one tile per cluster): announce its bytes now, before any
+    // CTA of the cluster can send.
+    if (csk > 0) mbar_arrive_expect_tx(bar_inbox, p.inbox_tx);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -494,6 +553,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     } else {
       named_bar_sync(3, T::THREADS);
     }
+    // Cluster split-K: the other CTAs of the cluster will write into this CTA's inbox and credit
+    // its inbox barrier.  Every thread announces here that the barrier exists and collects the
+    // same announcement of the whole cluster later, where it costs nothing: the loading and
+    // issuing warps after their loops, the epilogue warps just before they send.
+    if (csk > 0) cluster_arrive();
   } else {
     __syncthreads();
     // Both CTAs' barriers must exist before either one signals the other.
@@ -514,22 +578,27 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // launch may begin its own set-up on SMs that fall idle from here on.
   grid_launch_dependents();
 
-  // Cluster split-K: the cluster holds `csk` CTAs (CTA pairs when CG == 2), one per k-split
-  // of the cluster's tile.
-  const int csk = (T::EPI != EPI_SWIGLU && !T::LEAN) ? p.cluster_split : 0;
   const int csk_rank = csk > 0 ? static_cast<int>(cluster_ctarank()) / CG : 0;
-  const int ctas_per_unit = CG * (csk > 0 ? csk : 1);
-  const int first_unit = blockIdx.x / ctas_per_unit;
-  const int unit_stride = gridDim.x / ctas_per_unit;
+  const int first_unit = static_cast<int>(blockIdx.x >> p.ctas_per_unit_log2);
+  const int unit_stride = static_cast<int>(gridDim.x >> p.ctas_per_unit_log2);
 
   // The producer and MMA warps run their loops with all 32 lanes (addresses,
   // coordinates and descriptors are warp-uniform, which lets the compiler keep them
   // in uniform registers) and only one elected lane issues the asynchronous
   // instructions.
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == T::PRODUCER2_WARP) {
+    // ------------------------------------------------------------ TMA producers
+    // Two warps, each filling every other ring slot (both operands of it).  One thread can start
+    // a TMA tile load only every ~215 cycles, whatever the size of the box (measured on B200: 8
+    // to 128 rows of 128 bytes alike; two threads of different warps reach twice the rate).  With
+    // two loads per k-block a single producer holds every schedule to ~430 cycles per k-block:
+    // no tile narrower than 256 x 256 per CTA pair could feed its MMAs (256 x 128 pairs ran at
+    // 433 cycles per k-block against 256 tensor cycles) and a small-M weight stream could not go
+    // faster than one 16 KB slab per 430 cycles per SM.
     // With debug bit 0 set nothing is ever loaded: the MMA warp's wait for operands runs
     // out and the launch ends with ST_TIMEOUT_FULL in the status word.
+    const uint32_t prod_id = (warp == 0) ? 0u : 1u;
+    uint32_t slot_count = 0;  // ring slots this CTA has used so far, over all its units
     const bool issuer = elect_one() && (p.debug_flags & 1) == 0;
     const uint64_t pol_a = make_policy(p.l2_hint_a);
     const uint64_t pol_b = make_policy(p.l2_hint_b);
@@ -564,54 +633,86 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         // kernel, but its first operands may be asked into L2 (a prefetch delivers no data, and
         // L2 stays coherent with whatever that launch still writes): the loads issued after the
         // wait then find them there instead of paying the DRAM latency with an empty ring.
+        // A prefetch occupies the issuing thread as long as a load does, so each producer asks for
+        // the k-blocks it will load itself, and only for the operands worth it (the large ones).
         if (issuer) {
-          for (int kb = w.kb0; kb < w.kb1 && kb < w.kb0 + p.early_prefetch; ++kb) prefetch_l2(kb);
+          for (int i = 0; i < p.early_prefetch && w.kb0 + i < w.kb1; ++i) {
+            if (((slot_count + static_cast<uint32_t>(i / group)) & 1u) != prod_id) continue;
+            const int kb = w.kb0 + i;
+            if (p.early_operands & 1) tma_prefetch_l2_3d(&tm_a, kb * T::BK, w.m0, w.batch);
+            if (p.early_operands & 2) {
+              tma_prefetch_l2_3d(tm_b_mine, kb * T::BK, b_row, b_batch);
+              if constexpr (T::EPI == EPI_SWIGLU && CG == 1) tma_prefetch_l2_3d(&tm_b2, kb * T::BK, b_row, 0);
+            }
+          }
         }
         grid_dependency_wait();
         dependency_met = true;
 #ifdef AYLA_B200_TRACE
-        if (stamps != nullptr && lane == 0) stamps[14] = static_cast<long long>(global_timer_ns());
+        if (stamps != nullptr && lane == 0 && prod_id == 0) stamps[14] = static_cast<long long>(global_timer_ns());
 #endif
       }
-      if (issuer && pf > 0) {
+      if (issuer && pf > 0 && prod_id == 0) {
         for (int kb = w.kb0; kb < w.kb1 && kb < w.kb0 + pf; ++kb) prefetch_l2(kb);
       }
-      for (int kb = w.kb0; kb < w.kb1; ++kb) {
-        AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
-        if (issuer) {
-#ifdef AYLA_B200_TRACE
-          if (stamps != nullptr && !first_issue_stamped) {
-            stamps[12] = static_cast<long long>(global_timer_ns());
-            first_issue_stamped = true;
-          }
-#endif
-          const uint32_t full_bar = full_bar0 + stage * 8;
-          if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, p.stage_tx);
-          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
-          const uint32_t sb = sa + T::A_BYTES;
-          tma_load_3d<CG>(sa, &tm_a, full_bar, kb * T::BK, w.m0, w.batch, pol_a);
-          if constexpr (T::EPI == EPI_SWIGLU && CG == 1) {
-            // Accumulator columns [0,128) = gate, [128,256) = up.
-            tma_load_3d<CG>(sb, &tm_b, full_bar, kb * T::BK, b_row, 0, pol_b);
-            tma_load_3d<CG>(sb + T::B_BYTES / 2, &tm_b2, full_bar, kb * T::BK, b_row, 0, pol_b);
-          } else {
-            // Pair + SwiGLU: the leader's half of the B tile is gate, the peer's half is up.
-            tma_load_3d<CG>(sb, tm_b_mine, full_bar, kb * T::BK, b_row, b_batch, pol_b);
-          }
-          if (pf > 0 && kb + pf < w.kb1) prefetch_l2(kb + pf);
+      // One ring slot holds `group` consecutive k-blocks (one barrier pair for all of them): the
+      // hand-over of a slot between the warps costs a couple of hundred cycles whatever it holds.
+      for (int kb = w.kb0; kb < w.kb1; kb += group, ++slot_count) {
+        const bool mine = (slot_count & 1u) == prod_id;  // the other producer fills the slots in between
+        if (mine) {
+          AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_empty + stage * 8, phase ^ 1, ST_TIMEOUT_EMPTY))
         }
-        if (++stage == STAGES) {
+#ifdef AYLA_B200_TRACE
+        if (issuer && mine && stamps != nullptr && !first_issue_stamped && prod_id == 0) {
+          stamps[12] = static_cast<long long>(global_timer_ns());
+          first_issue_stamped = true;
+        }
+#endif
+        if (issuer && mine) {
+          const uint32_t full_bar = full_bar0 + stage * 8;
+          const int blocks = min(group, w.kb1 - kb);  // a unit may end in the middle of a slot
+#ifdef AYLA_B200_TUNE
+          if (p.debug_flags & 4) {  // tuning builds: hand the slot over without loading anything
+            if (is_leader) mbar_arrive(bar_full + stage * 8);
+          } else
+#endif
+          {
+            if (is_leader) mbar_arrive_expect_tx(bar_full + stage * 8, p.stage_tx * static_cast<uint32_t>(blocks));
+#pragma unroll
+            for (int g = 0; g < group; ++g) {
+              if (g < blocks) {
+                const uint32_t sa = smem_base + stage * T::SLOT_BYTES + g * T::STAGE_BYTES;
+                const uint32_t sb = sa + T::A_BYTES;
+                const int k0 = (kb + g) * T::BK;
+                tma_load_3d<CG>(sa, &tm_a, full_bar, k0, w.m0, w.batch, pol_a);
+                if constexpr (T::EPI == EPI_SWIGLU && CG == 1) {
+                  // Accumulator columns [0,128) = gate, [128,256) = up.
+                  tma_load_3d<CG>(sb, &tm_b, full_bar, k0, b_row, 0, pol_b);
+                  tma_load_3d<CG>(sb + T::B_BYTES / 2, &tm_b2, full_bar, k0, b_row, 0, pol_b);
+                } else {
+                  // Pair + SwiGLU: the leader's half of the B tile is gate, the peer's half is up.
+                  tma_load_3d<CG>(sb, tm_b_mine, full_bar, k0, b_row, b_batch, pol_b);
+                }
+                if (pf > 0 && kb + g + pf < w.kb1) prefetch_l2(kb + g + pf);
+              }
+            }
+          }
+        }
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1;
         }
       }
     }
-    AYLA_TRACE_END(0)
-    if (csk > 0) {
-      // Cluster barriers count every thread of the cluster: keep step with the two the
-      // epilogue warps use around the exchange of partial tiles.
-      cluster_arrive();
-      cluster_wait();
+#ifdef AYLA_B200_TRACE
+    if (prod_id == 0) {
+      AYLA_TRACE_END(0)
+    }
+#endif
+    if (CG == 1 && csk > 0) cluster_wait();
+    if (csk > 0 && p.inbox_in_ring) {
+      // A cluster barrier counts every thread of the cluster: keep step with the one the
+      // epilogue warps use before they send their partial tiles.
       cluster_arrive();
       cluster_wait();
     }
@@ -627,6 +728,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #ifdef AYLA_B200_TRACE
       bool first_operands_stamped = false;
       bool first_unit_of_cta = true;
+      long long tr_fence = 0, tr_issue = 0, tr_commit = 0, tr_iters = 0;
 #endif
       AYLA_TRACE_BEGIN
       UnitCursor<T> cursor(p, first_unit, unit_stride, 0, csk_rank);
@@ -638,7 +740,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const uint32_t tmem_d = tmem_base + acc * BN;
         const uint32_t unit_idesc = w.is_narrow ? p.idesc_narrow : idesc;
         const int nkb = w.kb1 - w.kb0;
-        for (int i = 0; i < nkb; ++i) {
+        for (int i = 0; i < nkb; i += group) {
           AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL))
 #ifdef AYLA_B200_TRACE
           if (stamps != nullptr && lane == 0 && !first_operands_stamped) {
@@ -648,34 +750,67 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (stamps != nullptr && lane == 0 && first_unit_of_cta) {
             const int span = nkb, done = i;
             for (int qd = 1; qd <= 3; ++qd) {
-              if (span >= 4 && done == qd * span / 4) stamps[8 + qd] = static_cast<long long>(global_timer_ns());
+              if (span >= 4 && done <= qd * span / 4 && qd * span / 4 < done + group) {
+                stamps[8 + qd] = static_cast<long long>(global_timer_ns());
+              }
             }
           }
 #endif
+#ifdef AYLA_B200_TRACE
+          const long long tr_a = clock64();
+#endif
           tc_fence_after_sync();
+#ifdef AYLA_B200_TRACE
+          const long long tr_b = clock64();
+          tr_fence += tr_b - tr_a;
+#endif
           if (issuer) {
-            // Stage offset and the +32 bytes per 16-element K step, both in the
-            // descriptor's 16-byte address units.
-            const uint32_t stage_off = stage * (T::STAGE_BYTES >> 4);
+            // Slot offset and the +32 bytes per 16-element K step, both in the descriptor's
+            // 16-byte address units.
+            const uint32_t slot_off = stage * (T::SLOT_BYTES >> 4);
+            const int blocks = min(group, nkb - i);  // a unit may end in the middle of a slot
+#ifdef AYLA_B200_TUNE
+            if ((p.debug_flags & 8) == 0)
+#endif
+            {
 #pragma unroll
-            for (int k4 = 0; k4 < T::BK / 16; ++k4) {
-              umma_f16<CG>(tmem_d, desc_a0 + (stage_off + 2 * k4), desc_b0 + (stage_off + 2 * k4), unit_idesc,
-                           (i > 0 || k4 > 0) ? 1u : 0u);
+              for (int g = 0; g < group; ++g) {
+                if (g < blocks) {
+#pragma unroll
+                  for (int k4 = 0; k4 < T::BK / 16; ++k4) {
+                    const uint32_t off = slot_off + g * (T::STAGE_BYTES >> 4) + 2 * k4;
+                    umma_f16<CG>(tmem_d, desc_a0 + off, desc_b0 + off, unit_idesc, (i + g > 0 || k4 > 0) ? 1u : 0u);
+                  }
+                }
+              }
             }
+#ifdef AYLA_B200_TRACE
+            const long long tr_c = clock64();
+            tr_issue += tr_c - tr_b;
+#endif
+#ifdef AYLA_B200_TUNE
+            if (p.debug_flags & 16) {
+              mbar_arrive(bar_empty + stage * 8);
+            } else
+#endif
             if constexpr (CG == 1) {
               umma_commit_1cta(bar_empty + stage * 8);
             } else {
               umma_commit_2cta(bar_empty + stage * 8, pair_mask);
             }
-            if (i == nkb - 1) {
+            if (i + group >= nkb) {
               if constexpr (CG == 1) {
                 umma_commit_1cta(bar_acc_full + acc * 8);
               } else {
                 umma_commit_2cta(bar_acc_full + acc * 8, pair_mask);
               }
             }
+#ifdef AYLA_B200_TRACE
+            tr_commit += clock64() - tr_c;
+            ++tr_iters;
+#endif
           }
-          if (++stage == STAGES) {
+          if (++stage == n_stages) {
             stage = 0;
             phase ^= 1;
           }
@@ -691,11 +826,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       AYLA_TRACE_END(1)
 #ifdef AYLA_B200_TRACE
       if (stamps != nullptr && lane == 0) stamps[3] = static_cast<long long>(global_timer_ns());
+      if (p.trace != nullptr && issuer) {
+        p.trace[blockIdx.x * 16 + 12] = tr_fence;
+        p.trace[blockIdx.x * 16 + 13] = tr_issue;
+        p.trace[blockIdx.x * 16 + 14] = tr_commit;
+        p.trace[blockIdx.x * 16 + 15] = tr_iters;
+      }
 #endif
     }
-    if (csk > 0) {
-      cluster_arrive();
-      cluster_wait();
+    if (CG == 1 && csk > 0) cluster_wait();
+    if (csk > 0 && p.inbox_in_ring) {
       cluster_arrive();
       cluster_wait();
     }
@@ -903,19 +1043,24 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (csk > 0) {
         // ---- cluster split-K: S CTAs of the cluster (those with this CTA's place in its
         // pair) hold the S partial sums of this 128-row tile.  Each owns BN / S columns of
-        // it: every CTA sends each owner its partial of the owner's columns through
-        // distributed shared memory (into the operand ring, idle by now), then each owner
-        // adds the S partials in split order and stores.
+        // it: every CTA sends each owner its partial of the owner's columns with asynchronous
+        // stores into the owner's inbox (distributed shared memory), each store crediting the
+        // owner's inbox barrier with its bytes; an owner waits for that barrier alone, adds
+        // the S partials in split order and stores.  Nobody waits for a sender's stores but
+        // their receiver.
         if constexpr (T::EPI != EPI_SWIGLU) {
           const int slice_cols = BN / csk;
           const int slice_shift = __ffs(slice_cols) - 1;
           const int slice_c4 = slice_cols >> 2;
-          const uint32_t exch = smem_u32(smem);
+          const uint32_t exch = smem_u32(smem) + p.inbox_offset;
           // A CTA keeps its own partial of its own columns in TMEM (no trip through shared
           // memory) whenever a 32-column TMEM load never straddles two owners.
           const bool own_in_tmem = slice_cols >= CHUNK_COLS;
-          cluster_arrive();  // every CTA's MMAs are done: no ring is being read any more
-          cluster_wait();
+          if constexpr (CG == 1) cluster_wait();  // every CTA of the cluster has its inbox barrier ready
+          if (p.inbox_in_ring) {
+            cluster_arrive();  // every CTA's MMAs are done: no ring is being read any more
+            cluster_wait();
+          }
 #ifdef AYLA_B200_TRACE
           if (stamps != nullptr && warp == 2 && lane == 0) stamps[6] = static_cast<long long>(global_timer_ns());
 #endif
@@ -926,11 +1071,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               const int owner = col >> slice_shift;
               if (own_in_tmem && owner == csk_rank) continue;
               const int c4 = (col - (owner << slice_shift)) >> 2;
+              const uint32_t owner_cta = static_cast<uint32_t>(owner * CG) + cta_rank;
+              // An owner that keeps its own partial in TMEM has no inbox slot for itself.
+              const int slot = (own_in_tmem && csk_rank > owner) ? csk_rank - 1 : csk_rank;
               const uint32_t dst =
-                  map_to_cta(exch + ((csk_rank * slice_c4 + c4) * 128 + row_in_tile) * 16,
-                             static_cast<uint32_t>(owner * CG) + cta_rank);
-              st_cluster_v4(dst, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                  map_to_cta(exch + ((slot * slice_c4 + c4) * 128 + row_in_tile) * 16, owner_cta);
+              st_async_v4(dst, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]),
+                          map_to_cta(bar_inbox, owner_cta));
             }
           };
           {
@@ -967,12 +1115,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               send_chunk(pending, ra);
             }
           }
-          cluster_arrive();  // all partials delivered
-          cluster_wait();
+#ifdef AYLA_B200_TRACE
+          if (stamps != nullptr && warp == 2 && lane == 0) stamps[15] = static_cast<long long>(global_timer_ns());
+#endif
+          // The partials of this CTA's columns have all landed when the inbox barrier completes.
+          bw.wait(bar_inbox, 0, ST_TIMEOUT_INBOX);
 #ifdef AYLA_B200_TRACE
           if (stamps != nullptr && warp == 2 && lane == 0) stamps[7] = static_cast<long long>(global_timer_ns());
 #endif
-          const float4* mine = reinterpret_cast<const float4*>(smem);
+          const float4* mine = reinterpret_cast<const float4*>(smem + p.inbox_offset);
           const int row = w.m0 + row_in_tile;
           if (own_in_tmem) {
             // Sum, in split order, the partials of this CTA's columns: its own from TMEM,
@@ -987,7 +1138,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     x = make_float4(__uint_as_float(own[4 * j]), __uint_as_float(own[4 * j + 1]),
                                     __uint_as_float(own[4 * j + 2]), __uint_as_float(own[4 * j + 3]));
                   } else {
-                    x = mine[(s * slice_c4 + lc * 8 + j) * 128 + row_in_tile];
+                    x = mine[((s > csk_rank ? s - 1 : s) * slice_c4 + lc * 8 + j) * 128 + row_in_tile];
                   }
                   sum.x += x.x;
                   sum.y += x.y;

@@ -20,6 +20,7 @@ struct LaunchArgs {
 
 struct KernelEntry {
   int tile_n, cta_group, epilogue, transposed_out, stages, smem_bytes;
+  int kb_per_slot;  // k-blocks one ring slot holds
   int activation;  // 1 = the variant whose epilogue applies the launch's activation
   int lean;        // 1 = the variant without the k-split epilogues
   const void* func;
@@ -32,7 +33,7 @@ template <int BN, int CG, int EPI, bool TR>
 constexpr int max_stages() {
   using T1 = GemmTraits<BN, CG, EPI, TR, 1>;
   const int fixed = T1::STORE_BYTES + T1::BIAS_BYTES + T1::MISC_BYTES;
-  const int s = (kMaxSmem - fixed) / T1::STAGE_BYTES;
+  const int s = (kMaxSmem - fixed) / T1::SLOT_BYTES;
 #ifdef AYLA_B200_STAGE_CAP
   return s > AYLA_B200_STAGE_CAP ? AYLA_B200_STAGE_CAP : s;
 #else
@@ -79,6 +80,7 @@ KernelEntry make_entry() {
   e.transposed_out = TR ? 1 : 0;
   e.stages = T::STAGES;
   e.smem_bytes = T::SMEM_BYTES;
+  e.kb_per_slot = T::KB_PER_SLOT;
   e.activation = ACT ? 1 : 0;
   e.lean = LEAN ? 1 : 0;
   e.func = reinterpret_cast<const void*>(&gemm_sm100_kernel<T>);

@@ -46,6 +46,17 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, float a, fl
                : "memory");
 }
 
+// 16-byte asynchronous store into the shared memory of a CTA of the cluster (this one included):
+// when the data has landed, `cluster_mbar` (an mbarrier in the same destination CTA) is credited
+// with 16 bytes of its pending transaction count.  The sender does not wait for anything.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, float a, float b, float c, float d,
+                                            uint32_t cluster_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
+                   cluster_addr),
+               "f"(a), "f"(b), "f"(c), "f"(d), "r"(cluster_mbar)
+               : "memory");
+}
+
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
