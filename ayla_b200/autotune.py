@@ -232,6 +232,19 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
         ranked = [(name, times[name]) for name in order + rest]
         for name in top:
             configs[name] = dict(configs[name], sustained_us=round(sustained[name] * 1e3, 2))
+    if flops / nbytes < 250.0 or flops < 5e10:
+        # Final pass (everything the sustained-regime pass did not order): the three fastest again, alone
+        # with cuBLAS.  In the big interleaved passes a launch meets whatever the forty other schedules
+        # left in L2, and eviction hints in particular can rank differently there than between two arms
+        # (C3a: both operands evict-first read 110 us among forty candidates, 140 us next to cuBLAS alone).
+        top = [name for name, _ in ranked[:3]]
+        final = time_interleaved({**{name: make(configs[name]) for name in top}, "torch": cublas}, launches, rounds)
+        torch_ms = final.pop("torch")
+        for name in top:
+            times[name] = final[name]
+        order = sorted(top, key=final.__getitem__)
+        rest = [(name, ms) for name, ms in ranked if name not in top]
+        ranked = [(name, times[name]) for name in order] + rest
     results = [dict(config=configs[name], us=ms * 1e3, tflops=flops / ms / 1e9, gbs=nbytes / ms / 1e6,
                     percentage_of_torch=100.0 * torch_ms / ms) for name, ms in ranked]
     del sets
