@@ -44,6 +44,47 @@ def test_place_gathered_panel_unpermutes():
     assert not out[:2].any() and not out[5:].any()
 
 
+def test_overlap_plan_orders_exactly_what_double_buffering_needs():
+    plan = sharded.overlap_plan(5, "nccl")
+    kinds = [(s.kind, s.panel) for s in plan]
+    assert kinds[:6] == [("gemm", 0), ("gather", 0), ("place", 0), ("gemm", 1), ("gather", 1), ("place", 1)]
+    at = {(s.kind, s.panel): i for i, s in enumerate(plan)}
+    for i in range(5):
+        assert plan[at["gemm", i]].stream == "main" and plan[at["gather", i]].stream == "comm"
+        assert plan[at["place", i]].stream == "place" and plan[at["gemm", i]].buf == i % 2
+        assert at["gemm", i] in plan[at["gather", i]].after          # gather after its GEMM
+        assert at["gather", i] in plan[at["place", i]].after         # placement after its gather
+        if i >= 2:
+            assert at["gather", i - 2] in plan[at["gemm", i]].after  # local buffer reuse
+            assert at["place", i - 2] in plan[at["gather", i]].after  # gather buffer reuse
+    # every dependency points backwards: the plan can be issued to streams in list order
+    assert all(dep < i for i, s in enumerate(plan) for dep in s.after)
+    dma = sharded.overlap_plan(3, "dma")
+    assert [s.kind for s in dma] == ["gemm", "push"] * 3 and dma[4].after == (1,)
+    with pytest.raises(ValueError):
+        sharded.overlap_plan(3, "smoke signals")
+
+
+def test_run_plan_in_order_respects_streams_and_dependencies():
+    import random
+
+    plan = sharded.overlap_plan(6, "nccl")
+    rng = random.Random(5)
+    for _ in range(20):
+        order = sharded.run_plan_in_order(plan, lambda step: None, pick=rng.choice)
+        assert sorted(order) == list(range(len(plan)))
+        position = {index: at for at, index in enumerate(order)}
+        for index, step in enumerate(plan):
+            assert all(position[dep] < position[index] for dep in step.after)
+        for stream in ("main", "comm", "place"):
+            on_stream = [i for i in order if plan[i].stream == stream]
+            assert on_stream == sorted(on_stream)
+    # a plan that waits on something that never runs is reported, not spun on
+    broken = [sharded.Step("gemm", 0, 0, "main", (1,)), sharded.Step("gather", 0, 0, "comm", (0,))]
+    with pytest.raises(RuntimeError, match="deadlock"):
+        sharded.run_plan_in_order(broken, lambda step: None)
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -69,6 +110,17 @@ def _worker(rank: int, world: int, port: int, results):
             lambda ap, bs, local: local.copy_(O.gemm_ref("mm", torch.bfloat16, ap, bs)), panel_rows=64)
         ok_mm = torch.equal(out.view(torch.int16), full.view(torch.int16))
 
+        # the overlapped runner's plan, its buffers reused across panels, executed in a random order
+        # that respects the plan's dependencies only (a different order on every rank)
+        import random
+
+        out2 = torch.full((m, n), float("nan"), dtype=torch.bfloat16)
+        rng = random.Random(100 + rank)
+        order = sharded.n_sharded_mm_by_plan(
+            a, bt[col0:col0 + width].contiguous(), out2,
+            lambda ap, bs, local: local.copy_(O.gemm_ref("mm", torch.bfloat16, ap, bs)), panel_rows=24, pick=rng.choice)
+        ok_mm = ok_mm and torch.equal(out2.view(torch.int16), full.view(torch.int16)) and len(order) == 3 * 9
+
         # batch-sharded bmm: slices are independent; gather only to compare
         batch = 5
         a3 = torch.randn(batch, 40, 32, generator=g).bfloat16()
@@ -93,9 +145,9 @@ def _worker(rank: int, world: int, port: int, results):
         dist.destroy_process_group()
 
 
-def test_sharded_flows_on_two_gloo_ranks():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_flows_on_gloo_ranks(world):
     manager = mp.Manager()
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
-    assert dict(results) == {0: (True, True, True), 1: (True, True, True)}
+    assert dict(results) == {rank: (True, True, True) for rank in range(world)}
