@@ -205,6 +205,29 @@ def test_swiglu_on_a_concatenated_weight_spelled_as_two_slices_is_fused():
     assert tc.route_swiglu_concat(gm.graph) == 0
 
 
+def test_gated_decoder_block_body_is_routed_completely():
+    """The whole-graph driver's block body (gated attention output projection, SwiGLU on a
+    concatenated weight read as two slices, fused QKV): after the pass every GEMM is one of this
+    library's ops, the gate is fused into its GEMM and the MLP is the fused SwiGLU op."""
+    from ayla_b200.bench_torch_compile import gated_block_fn
+
+    tokens, hidden, attn, ffn, kv = 16, 64, 32, 48, 8
+    block = gated_block_fn(attn, ffn, kv)
+    cuda = "cuda"
+    specs = [((tokens, hidden), BF16, cuda), ((tokens, attn), BF16, cuda), ((tokens, hidden), BF16, cuda),
+             ((attn, hidden), BF16, cuda), ((hidden, attn), BF16, cuda), ((2 * ffn, hidden), BF16, cuda),
+             ((hidden, ffn), BF16, cuda), ((attn + 2 * kv, hidden), BF16, cuda)] + [((hidden,), BF16, cuda)] * 4
+    gm = trace(block, *specs)
+    assert targets(gm).count(aten.mm.default) == 5
+    tc.AylaRoutingPass()(gm.graph)
+    gm.graph.lint()
+    found = targets(gm)
+    assert aten.mm.default not in found
+    assert found.count(torch.ops.ayla.swiglu_bf16_fn.default) == 1
+    assert found.count(torch.ops.ayla.jit_mm_sigmoid_mul_bf16_fn.default) == 1
+    assert found.count(torch.ops.ayla.jit_mm_bf16_fn.default) == 3
+
+
 def test_every_op_the_pass_can_emit_is_registered_by_install():
     """On a hit in Inductor's code cache the pass never runs in the new process: the cached code
     names torch.ops.ayla.* ops, which must exist after install() alone."""
