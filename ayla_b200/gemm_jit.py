@@ -188,11 +188,13 @@ def _fallback_schedule(operation: str, dtype: str, m: int, n: int, k: int,
 class GemmLauncher:
     """One specialised ``(operation, dtype, shape, device)`` launch.
 
-    Owns the split-K workspace and the status word of its shape; both are
-    allocated here, at specialisation time, so that a launch itself allocates
-    nothing and can be captured in a CUDA graph.  Two launches of the same shape
-    that overlap on different streams would share that workspace; callers that
-    do so must serialise them.
+    Owns the split-K workspaces and the status word of its shape.  The workspace of the
+    stream that is current at specialisation time is allocated here, so that a launch
+    itself allocates nothing and can be captured in a CUDA graph.  A launch on another
+    stream gets a workspace of its own the first time that stream is used (two launches
+    of one shape that overlap on different streams would otherwise sum into each other's
+    partial tiles); that first use allocates, so it must happen outside graph capture --
+    inside capture it raises ``RuntimeError`` as a first call of a new shape does.
 
     The status word lives in pinned host memory (``_lib.StatusWord``): every call reads it
     before launching, without synchronising, and raises ``RuntimeError`` if an earlier
@@ -215,10 +217,15 @@ class GemmLauncher:
         with torch.cuda.device(index):
             _lib.init(index)
         need = _lib.workspace_bytes(self.config, operation, batch, m, n, k)
+        self._ws_bytes = need
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=device) if need else None
         self.status = _lib.StatusWord()
         self._ws_ptr = self.workspace.data_ptr() if self.workspace is not None else 0
         self._status_ptr = self.status.ptr
+        # stream handle -> (workspace tensor, argument tail); the first entry serves the stream current now
+        with torch.cuda.device(index):
+            self._home_stream = torch.cuda.current_stream().cuda_stream if need else None
+        self._per_stream: dict[int, tuple[torch.Tensor, tuple]] = {}
         self._debug = bool(os.environ.get("AYLA_B200_DEBUG"))
         # Everything that does not change from call to call, converted for the C call once.
         import ctypes
@@ -243,19 +250,37 @@ class GemmLauncher:
             a, bt, out = tensors
         if self.status.peek():
             self._report_timeout()
+        stream = torch.cuda.current_stream(self._device_index).cuda_stream
+        tail = self._tail
+        if self._ws_bytes and stream != self._home_stream:
+            tail = self._tail_for_stream(stream)
         # The library launches on the current device (the reference's launcher guards the device
         # the same way, ayla/ptx_runtime.py:268-275).
         if torch.cuda.current_device() != self._device_index:
             with torch.cuda.device(self._device_index):
                 code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), mul_ptr, out.data_ptr(),
-                                   *self._tail, torch.cuda.current_stream(self._device_index).cuda_stream)
+                                   *tail, stream)
         else:
             code = self._entry(*self._head, bias_ptr, a.data_ptr(), bt.data_ptr(), mul_ptr, out.data_ptr(),
-                               *self._tail, torch.cuda.current_stream(self._device_index).cuda_stream)
+                               *tail, stream)
         if code:
             _lib.check(code)
         if self._debug:
             self.check_status()
+
+    def _tail_for_stream(self, stream: int) -> tuple:
+        """The call arguments with the workspace that belongs to ``stream`` (allocated on first use)."""
+        entry = self._per_stream.get(stream)
+        if entry is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(
+                    f"jit_{self.operation}: the first launch of this k-split shape on a new stream allocates its "
+                    "workspace and cannot happen during CUDA graph capture; run it once on that stream before capturing")
+            workspace = torch.zeros(self._ws_bytes, dtype=torch.uint8, device=self.device)
+            batch, m, n, k, cfg, _, size, status = self._tail
+            entry = (workspace, (batch, m, n, k, cfg, workspace.data_ptr(), size, status))
+            self._per_stream[stream] = entry
+        return entry[1]
 
     def _report_timeout(self) -> None:
         code = self.status.peek()
@@ -263,6 +288,8 @@ class GemmLauncher:
             torch.cuda.current_stream().synchronize()  # nothing of the failed launch is still running
             if self.workspace is not None:
                 self.workspace.zero_()  # arrival counters a timed-out k-split leaves behind
+            for workspace, _ in self._per_stream.values():
+                workspace.zero_()
         self.status.clear()
         raise RuntimeError(
             f"jit_{self.operation}: device wait timed out (code {code & 0xFF}, CTA {code >> 8})"

@@ -195,6 +195,7 @@ def test_launcher_makes_its_own_device_current_for_the_launch(monkeypatch):
     launcher.status = types.SimpleNamespace(peek=lambda: 0)
     launcher._has_bias, launcher.gated, launcher._debug = False, False, False
     launcher._head, launcher._tail, launcher._device_index = (0, 1, 0), (), 1
+    launcher._ws_bytes, launcher._home_stream = 0, None
     launcher._entry = lambda *args: launches.append((current[0], args[-1])) or 0
     tensor = types.SimpleNamespace(data_ptr=lambda: 16)
     launcher(tensor, tensor, tensor)
@@ -220,6 +221,7 @@ def test_launcher_reports_a_timed_out_launch_before_the_next_one(monkeypatch):
     launcher.operation = "mm"
     launcher._has_bias, launcher.gated, launcher._debug = False, False, False
     launcher._head, launcher._tail, launcher._device_index = (0, 1, 0), (), 0
+    launcher._ws_bytes, launcher._home_stream, launcher._per_stream = 0, None, {}
     launches = []
     launcher._entry = lambda *args: launches.append(args) or 0
 
@@ -243,3 +245,56 @@ def test_launcher_reports_a_timed_out_launch_before_the_next_one(monkeypatch):
     assert launches == [] and cleared == ["workspace"] and word[0] == 0
     launcher(tensor, tensor, tensor)
     assert len(launches) == 1
+
+
+def test_launcher_gives_every_stream_its_own_k_split_workspace(monkeypatch):
+    """Two launches of one k-split shape that overlap on different streams must not share partial
+    sums: the launcher passes the workspace of the stream it launches on, allocating one the first
+    time a stream is used (and refusing to do that during graph capture)."""
+    import types
+
+    from ayla_b200.gemm_jit import GemmLauncher
+
+    current_stream = [7]
+    capturing = [False]
+    allocated = []
+
+    def fake_zeros(size, dtype=None, device=None):
+        allocated.append(size)
+        return types.SimpleNamespace(data_ptr=lambda n=len(allocated): 1000 * n, zero_=lambda: None)
+
+    class NoGuard:
+        def __init__(self, index):
+            pass
+
+        def __enter__(self):
+            pass
+
+        def __exit__(self, *exc):
+            pass
+
+    monkeypatch.setattr(torch, "zeros", fake_zeros)
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    monkeypatch.setattr(torch.cuda, "device", NoGuard)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda index=None: types.SimpleNamespace(cuda_stream=current_stream[0]))
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: capturing[0])
+    launcher = object.__new__(GemmLauncher)
+    launcher.status = types.SimpleNamespace(peek=lambda: 0)
+    launcher.operation, launcher.device = "mm", "cuda:0"
+    launcher._has_bias, launcher.gated, launcher._debug = False, False, False
+    launcher._head, launcher._device_index = (0, 1, 0), 0
+    launcher._tail = (1, 256, 256, 2048, "cfg", 500, 4096, 9)
+    launcher._ws_bytes, launcher._home_stream, launcher._per_stream = 4096, 7, {}
+    seen = []
+    launcher._entry = lambda *args: seen.append((args[-1], args[-4])) or 0   # (stream, workspace pointer)
+    tensor = types.SimpleNamespace(data_ptr=lambda: 16)
+    launcher(tensor, tensor, tensor)
+    current_stream[0] = 8
+    launcher(tensor, tensor, tensor)
+    launcher(tensor, tensor, tensor)
+    current_stream[0] = 7
+    launcher(tensor, tensor, tensor)
+    assert seen == [(7, 500), (8, 1000), (8, 1000), (7, 500)] and allocated == [4096]
+    current_stream[0], capturing[0] = 9, True
+    with pytest.raises(RuntimeError, match="graph capture"):
+        launcher(tensor, tensor, tensor)
