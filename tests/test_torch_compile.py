@@ -205,6 +205,19 @@ def test_swiglu_on_a_concatenated_weight_spelled_as_two_slices_is_fused():
     assert tc.route_swiglu_concat(gm.graph) == 0
 
 
+def test_swiglu_fusion_is_declined_where_its_column_tiles_fill_the_sms_badly():
+    assert tc._swiglu_pays(8, 14336) and tc._swiglu_pays(4096, 19968) and tc._swiglu_pays(64, 128 * 148)
+    assert not tc._swiglu_pays(8, 19968) and not tc._swiglu_pays(64, 128 * 149)
+
+    def block(x, w):
+        gate, up = torch.mm(x, w.t()).chunk(2, dim=-1)
+        return torch.nn.functional.silu(gate) * up
+
+    gm = trace(block, ((8, 64), BF16, "cuda"), ((2 * 19968, 64), BF16, "cuda"))
+    assert tc.route_swiglu_concat(gm.graph) == 0       # left to the plain GEMM route
+    assert tc.route_gemms(gm.graph) == 1
+
+
 def test_gated_decoder_block_body_is_routed_completely():
     """The whole-graph driver's block body (gated attention output projection, SwiGLU on a
     concatenated weight read as two slices, fused QKV): after the pass every GEMM is one of this
