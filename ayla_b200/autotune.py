@@ -106,7 +106,7 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
     return out
 
 
-def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: int = 5) -> dict:
+def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: int = 5, light: bool = False) -> dict:
     dev = "cuda"
     td = torch.bfloat16 if dtype == "bfloat16" else torch.float16
     lead = (batch,) if op == "bmm" else ()
@@ -196,7 +196,8 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
             tweaks += [dict(group_m=g) for g in (2, 4, 16) if g != base.get("group_m")]
         return tweaks
 
-    refine_pass(hint_tweaks, "r")
+    if not light:
+        refine_pass(hint_tweaks, "r")
     if flops / nbytes < 250.0:
         # Third pass, HBM-bound shapes (ridge ~ 248 flop/byte at the measured peaks): how many k-blocks of
         # its first tile a CTA asks into L2 before it waits for the preceding launch.
@@ -205,7 +206,7 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
             return [dict(early_prefetch=e) for e in (4, 8, 12, 16, 24, 32) if e <= share]
 
         refine_pass(early_tweaks, "e")
-    elif flops >= 5e10:
+    elif flops >= 5e10 and not light:
         # Large compute-bound shapes run for seconds under the power cap in real use, where the schedules
         # rank differently than in short bursts (the L2 hints that keep operands resident save power).
         # Rank the three fastest again in that regime: back-to-back launches for a quarter of a second each,
@@ -232,7 +233,7 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
         ranked = [(name, times[name]) for name in order + rest]
         for name in top:
             configs[name] = dict(configs[name], sustained_us=round(sustained[name] * 1e3, 2))
-    if flops / nbytes < 250.0 or flops < 5e10:
+    if flops / nbytes < 250.0 or flops < 5e10 or light:
         # Final pass (everything the sustained-regime pass did not order): the three fastest again, alone
         # with cuBLAS.  In the big interleaved passes a launch meets whatever the forty other schedules
         # left in L2, and eviction hints in particular can rank differently there than between two arms
@@ -267,7 +268,7 @@ def _write_done(done: dict[tuple, dict], out_path: Path) -> None:
     os.replace(tmp, out_path)
 
 
-def measure(shapes, out_path: Path, rounds: int = 5, progress_path: Path | None = None) -> None:
+def measure(shapes, out_path: Path, rounds: int = 5, progress_path: Path | None = None, light: bool = False) -> None:
     """Measure every shape not yet in ``out_path``, rewriting the file atomically after each one.
     ``progress_path``, if given, names the shape being measured (for the supervising process of
     :func:`measure_isolated`)."""
@@ -278,7 +279,7 @@ def measure(shapes, out_path: Path, rounds: int = 5, progress_path: Path | None 
             continue
         if progress_path is not None:
             progress_path.write_text(json.dumps(list(shape)))
-        row = tune_shape(*shape, rounds=rounds)
+        row = tune_shape(*shape, rounds=rounds, light=light)
         done[tuple(shape)] = row
         if not row["results"]:
             print(f"[autotune] {shape}: no valid schedule", flush=True)
@@ -290,7 +291,7 @@ def measure(shapes, out_path: Path, rounds: int = 5, progress_path: Path | None 
 
 
 def measure_isolated(shapes, out_path: Path, shapes_file: Path, rounds: int = 3,
-                     per_shape_timeout: float = 120.0) -> None:
+                     per_shape_timeout: float = 120.0, light: bool = False) -> None:
     """The sweep in a worker process, supervised from this one (which never touches the GPU).
 
     The reference's harness spawns one process per shape with a timeout and resumes finished shapes
@@ -312,7 +313,8 @@ def measure_isolated(shapes, out_path: Path, shapes_file: Path, rounds: int = 3,
             return
         progress.unlink(missing_ok=True)
         worker = subprocess.Popen([sys.executable, "-m", "ayla_b200.autotune", "--worker", "--out", str(out_path),
-                                   "--shapes-file", str(shapes_file), "--rounds", str(rounds)])
+                                   "--shapes-file", str(shapes_file), "--rounds", str(rounds)]
+                                  + (["--light"] if light else []))
         last_shape, since = None, time.monotonic()
         failed = None
         while worker.poll() is None:
@@ -400,6 +402,8 @@ def main() -> None:
     parser.add_argument("--isolate", action="store_true", help="measure in a supervised worker process")
     parser.add_argument("--rounds", type=int, default=5)
     parser.add_argument("--limit", type=int, default=0, help="corpus: only the N most frequent shapes (0 = all)")
+    parser.add_argument("--light", action="store_true",
+                        help="no eviction-hint pass and no sustained-regime pass (the broad corpus sweep)")
     parser.add_argument("--worker", action="store_true", help=argparse.SUPPRESS)
     parser.add_argument("--shapes-file", default=None, help=argparse.SUPPRESS)
     args = parser.parse_args()
@@ -410,7 +414,7 @@ def main() -> None:
     out.parent.mkdir(parents=True, exist_ok=True)
     if args.worker:
         shapes = [tuple(s) for s in json.loads(Path(args.shapes_file).read_text())]
-        measure(shapes, out, rounds=args.rounds, progress_path=out.with_suffix(".progress"))
+        measure(shapes, out, rounds=args.rounds, progress_path=out.with_suffix(".progress"), light=args.light)
         return
     shapes = []
     if args.shapes == "corpus":
@@ -426,9 +430,9 @@ def main() -> None:
     if args.isolate:
         shapes_file = out.with_suffix(".shapes")
         shapes_file.write_text(json.dumps([list(s) for s in shapes]))
-        measure_isolated(shapes, out, shapes_file, rounds=args.rounds)
+        measure_isolated(shapes, out, shapes_file, rounds=args.rounds, light=args.light)
     else:
-        measure(shapes, out, rounds=args.rounds)
+        measure(shapes, out, rounds=args.rounds, light=args.light)
 
 
 if __name__ == "__main__":
