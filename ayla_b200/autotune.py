@@ -98,6 +98,12 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
             if tiles * cta_group <= SM_COUNT:
                 for s in splits[:3]:
                     out.append(dict(base, split_k=s))
+                # Very deep reductions over a handful of tiles (weight gradients: K = tokens): split until the
+                # grid is full, as long as every split keeps at least eight k-blocks.
+                if tile_n <= 128:
+                    for s in (16, 32, 64, 128):
+                        if s not in splits[:3] and k_blocks >= 8 * s and tiles * s * cta_group <= 2 * SM_COUNT:
+                            out.append(dict(base, split_k=s))
                 for s in (2, 4, 8):
                     if tile_n != 192 and s * cta_group <= 4 and k_blocks >= 4 * s and tiles * s * cta_group <= 2 * SM_COUNT:
                         out.append(dict(base, split_k=s, cluster_split=1))
@@ -337,8 +343,20 @@ def measure_isolated(shapes, out_path: Path, shapes_file: Path, rounds: int = 3,
         print(f"[autotune] {stuck}: {reason}; restarting the worker", flush=True)
 
 
-def emit_table(results_path: Path, table_path: Path, keep: int = 3) -> None:
-    rows = json.loads(results_path.read_text())
+def emit_table(results_paths: list[Path], table_path: Path, keep: tuple[int, ...] = (3,)) -> None:
+    """Write the schedule table from one or more results files.  A shape present in several files takes
+    its rows from the first file that has it; ``keep[i]`` schedules per shape are kept from file i
+    (the last value serves the remaining files)."""
+    rows: list[dict] = []
+    seen: set[tuple] = set()
+    for index, path in enumerate(results_paths):
+        limit = keep[min(index, len(keep) - 1)]
+        for row in json.loads(path.read_text()):
+            key = tuple(row[k] for k in _KEY)
+            if key in seen:
+                continue
+            seen.add(key)
+            rows.append(dict(row, results=row["results"][:limit]))
     configs: list[dict] = []
     index: dict[str, int] = {}
     schedules: dict[tuple[str, str], dict[tuple[int, int, int, int], list[int]]] = {}
@@ -346,7 +364,7 @@ def emit_table(results_path: Path, table_path: Path, keep: int = 3) -> None:
         if not row["results"]:
             continue  # a shape whose measurement failed or that has no valid schedule
         picks = []
-        for res in row["results"][:keep]:
+        for res in row["results"]:
             entry = dict(res["config"])
             entry["us"] = round(res["us"], 2)
             entry["tflops"] = round(res["tflops"], 1)
@@ -398,7 +416,10 @@ def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--out", default="results/autotune.json")
     parser.add_argument("--shapes", default="all", choices=["all", "baseline", "sweep", "decoder", "large", "corpus"])
-    parser.add_argument("--emit", default=None, help="write the schedule table to this path instead of measuring")
+    parser.add_argument("--emit", default=None,
+                        help="write the schedule table to this path instead of measuring (--out may then list "
+                             "several results files, comma separated; the first file that has a shape wins)")
+    parser.add_argument("--emit-keep", default="3", help="schedules kept per shape, per results file (comma separated)")
     parser.add_argument("--isolate", action="store_true", help="measure in a supervised worker process")
     parser.add_argument("--rounds", type=int, default=5)
     parser.add_argument("--limit", type=int, default=0, help="corpus: only the N most frequent shapes (0 = all)")
@@ -407,10 +428,11 @@ def main() -> None:
     parser.add_argument("--worker", action="store_true", help=argparse.SUPPRESS)
     parser.add_argument("--shapes-file", default=None, help=argparse.SUPPRESS)
     args = parser.parse_args()
-    out = Path(args.out)
     if args.emit:
-        emit_table(out, Path(args.emit))
+        emit_table([Path(p) for p in args.out.split(",")], Path(args.emit),
+                   tuple(int(v) for v in args.emit_keep.split(",")))
         return
+    out = Path(args.out)
     out.parent.mkdir(parents=True, exist_ok=True)
     if args.worker:
         shapes = [tuple(s) for s in json.loads(Path(args.shapes_file).read_text())]

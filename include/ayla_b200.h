@@ -106,8 +106,10 @@ AYLA_B200_API int ayla_b200_init(int device);
  * with ayla_b200_default_config.  `workspace` is needed only when the schedule has
  * split_k > 1; it must hold ayla_b200_workspace_bytes(...) bytes, the first
  * ayla_b200_workspace_counter_bytes(...) of them zero before the first use (the
- * kernel leaves them zero).  `status`, if non-NULL, is a device uint32 the kernel
- * sets to a non-zero code when one of its bounded waits gives up; zero it first.
+ * kernel leaves them zero).  `status`, if non-NULL, is a uint32 the device can write
+ * (device memory, or pinned host memory, which the host can then read without
+ * synchronising); the kernel sets it to a non-zero code when one of its bounded
+ * waits gives up; zero it first.
  */
 AYLA_B200_API int ayla_b200_gemm(int op, int dtype, const void* bias, const void* a, const void* bt, void* out,
                    int64_t batch, int64_t m, int64_t n, int64_t k, const ayla_b200_config* cfg,
@@ -264,10 +266,12 @@ AYLA_B200_API int ayla_b200_kernel_info(int i, int32_t* tile_n, int32_t* cta_gro
 AYLA_B200_API void ayla_b200_set_wait_timeout_ms(int64_t ms);
 
 /*
- * Test hook for the failure path.  Bit 0: the TMA producer of every later launch issues no
- * loads, so the MMA warp's bounded wait for operands runs out (after the wait timeout) and the
- * launch ends normally with code 2 in `status` and garbage in `out`; the context stays usable.
- * 0 restores normal operation.
+ * Test hooks.  Bit 0: the TMA producers of every later launch issue no loads, so the MMA
+ * warp's bounded wait for operands runs out (after the wait timeout) and the launch ends
+ * normally with code 2 in `status` and garbage in `out`; the context stays usable.
+ * Bit 1: cluster split-K launches keep all their ring slots and let the inbox of partial sums
+ * overlay them (the form used when the ring could not spare the slots), so that both forms of
+ * the exchange can be compared on one shape.  0 restores normal operation.
  */
 AYLA_B200_API void ayla_b200_debug_set_flags(int flags);
 
