@@ -485,7 +485,9 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
     # The NCCL all-gather path: a small sweep of how many thread blocks NCCL may use against how many
     # SMs the GEMM leaves it, then the best pair again with its legs timed.
     sweep = []
-    choices = ((16, 16), (32, 32), (48, 48), (64, 64)) if world > 2 else ((16, 16),)
+    # (NCCL thread blocks, SMs left free): NCCL's blocks are small enough to share an SM, so fewer SMs than
+    # blocks may be set aside.
+    choices = ((32, 32), (32, 16), (48, 16), (64, 16), (64, 24)) if world > 2 else ((16, 16),)
     for max_ctas, reserve in choices:
         try:
             row = run_variant(f"nccl max_ctas={max_ctas} reserve={reserve}", "nccl", max_ctas=max_ctas, reserve_sms=reserve)
