@@ -454,6 +454,17 @@ def main() -> None:
         run_case(args)
         return
 
+    # Only the JSON line may reach stdout: libraries that write there from native code (NCCL prints its
+    # version at communicator creation) are sent to stderr until the line is printed.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line: dict) -> None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(line), flush=True)
+
     rank, world, local = dist_setup(args.gpus)
     from ayla_b200 import _lib, gemm_op
 
@@ -659,7 +670,7 @@ def main() -> None:
         suite_out = Path(args.suite_out)
         suite_out.parent.mkdir(parents=True, exist_ok=True)
         suite_out.write_text(json.dumps(rows, indent=1))
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def sharded_results(args, rank: int, world: int, device) -> dict:
