@@ -676,7 +676,7 @@ int launch_plan(const Plan& plan, const ayla_b200_config& c, const Problem& pr, 
   }
 #ifdef AYLA_B200_TRACE
   // Tuning builds: a schedule that needs no scratch lends the workspace to the per-CTA cycle counters.
-  if (plan.slabs == 0 && workspace != nullptr && workspace_bytes >= (4096 + static_cast<size_t>(plan.grid) * 16) * 8) {
+  if (plan.slabs == 0 && workspace != nullptr && workspace_bytes >= (4096 + static_cast<size_t>(plan.grid) * 64) * 8) {
     p.trace = reinterpret_cast<long long*>(workspace);
   }
 #endif

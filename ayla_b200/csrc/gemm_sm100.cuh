@@ -126,6 +126,18 @@ struct KernelParams {
 // Cycle accounting for tuning builds (-DAYLA_B200_TRACE): each role records the
 // cycles it spent inside barrier waits and its total loop time.
 #ifdef AYLA_B200_TRACE
+// One point of a CTA's timeline: this SM's cycle counter, kept in shared memory until the CTA leaves
+// (reading globaltimer costs some 0.15 us, and a store to global memory in flight delays the next
+// release at cluster scope: both moved the times they were meant to measure).  Entry (slot 0) and exit
+// (slot 5) also record globaltimer, in slots 32 and 33, which places the CTA's cycle counts on the time
+// base all SMs share.
+__device__ __forceinline__ void trace_stamp(long long* stamps, int slot) {
+  stamps[slot] = clock64();
+  if (slot == 0) stamps[32] = static_cast<long long>(global_timer_ns());
+  if (slot == 5) stamps[33] = static_cast<long long>(global_timer_ns());
+}
+#endif
+#ifdef AYLA_B200_TRACE
 #define AYLA_TRACE_BEGIN long long tr_wait = 0, tr_wait2 = 0, tr_wait3 = 0, tr_tmp = 0; const long long tr_t0 = clock64();
 #define AYLA_TRACE_WAIT(acc, stmt) tr_tmp = clock64(); stmt; acc += clock64() - tr_tmp;
 #define AYLA_TRACE_END(slot)                                          \
@@ -182,7 +194,12 @@ struct GemmTraits {
   static constexpr int STORE_BYTES = TRANS_OUT ? 0 : EPI_WARPS * STORE_BUF_BYTES;
   static constexpr int BIAS_BYTES = (EPI == EPI_BIAS && !TRANS_OUT) ? 2 * BN * 4 : 0;
   static constexpr int MISC_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * SLOT_BYTES + STORE_BYTES + BIAS_BYTES + MISC_BYTES;
+#ifdef AYLA_B200_TRACE
+  static constexpr int TRACE_BYTES = 40 * 8;  // the CTA's timeline stamps, copied out at exit
+#else
+  static constexpr int TRACE_BYTES = 0;
+#endif
+  static constexpr int SMEM_BYTES = STAGES * SLOT_BYTES + STORE_BYTES + BIAS_BYTES + MISC_BYTES + TRACE_BYTES;
   // Warps: 0 = first TMA producer, 1 = MMA issuer, 2..9 = epilogue, 10 = second TMA producer.
   static constexpr int PRODUCER2_WARP = 2 + EPI_WARPS;
   static constexpr int THREADS = 64 + EPI_WARPS * 32 + 32;
@@ -348,6 +365,15 @@ struct UnitCursor {
     return true;
   }
 
+  // True when at least n (1 or 2) more units follow the one `next` returned last.
+  __device__ __forceinline__ bool follows(int n) const {
+    if (p.stream_k) {
+      if (pos >= end) return false;
+      return n <= 1 || (pos / p.k_blocks + 1) * p.k_blocks < end;
+    }
+    return unit + (n - 1) * num_ctas < p.total_units;
+  }
+
   // Slab that holds contribution j (0 <= j < nsplit) to the tile of unit w.
   __device__ __forceinline__ int slab_of(const WorkUnit& w, int j) const {
     if (!p.stream_k) return w.slab0 + j;
@@ -484,15 +510,17 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 #ifdef AYLA_B200_TRACE
-  // Timeline of this CTA in globaltimer nanoseconds: entry, set-up done, first operands
-  // landed, last MMA committed, epilogue done, exit.
+  // Timeline of this CTA in cycles of its SM (see trace_stamp).
   // Slots: 0 entry, 1 set-up done, 2 first operands landed, 3 last MMA committed, 4 epilogue done, 5 exit,
   // 6/7 cluster split-K barriers, 8 SM id, 9-11 a quarter / half / three quarters of the CTA's first unit
   // issued, 12 first TMA load issued, 13 epilogue saw the first finished accumulator, 14 the preceding
-  // launch is complete (dependency wait returned).
-  long long* stamps = (p.trace != nullptr) ? p.trace + 4096 + blockIdx.x * 16 : nullptr;
+  // launch is complete (dependency wait returned), 15 split-k parts sent, 16 first accumulator chunk in
+  // registers, 17 last output chunk handed to the store path, 18-21 the first warp's 64-column groups done,
+  // 22/23 its first two chunks staged, 24 staging published to the async proxy, 25 bulk store issued.
+  long long* stamps = (p.trace != nullptr) ? reinterpret_cast<long long*>(smem_misc + T::MISC_BYTES) : nullptr;
   if (stamps != nullptr && threadIdx.x == 0) {
-    stamps[0] = static_cast<long long>(global_timer_ns());
+    for (int i = 0; i < 40; ++i) stamps[i] = 0;
+    trace_stamp(stamps, 0);
     uint32_t smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     stamps[8] = static_cast<long long>(smid) + 1;
@@ -557,17 +585,18 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // its inbox barrier.  Every thread announces here that the barrier exists and collects the
     // same announcement of the whole cluster later, where it costs nothing: the loading and
     // issuing warps after their loops, the epilogue warps just before they send.
-    if (csk > 0) cluster_arrive();
+    if (csk > 0) cluster_arrive_relaxed();
   } else {
     __syncthreads();
-    // Both CTAs' barriers must exist before either one signals the other.
-    cluster_arrive();
+    // Both CTAs' barriers must exist before either one signals the other (their initialisation
+    // was published by fence_mbar_init above).
+    cluster_arrive_relaxed();
     cluster_wait();
   }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 #ifdef AYLA_B200_TRACE
-  if (stamps != nullptr && threadIdx.x == 32) stamps[1] = static_cast<long long>(global_timer_ns());
+  if (stamps != nullptr && threadIdx.x == 32) trace_stamp(stamps, 1);
 #endif
 
   // Everything above touched only this launch's own shared memory, TMEM and parameters, and so
@@ -649,7 +678,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         grid_dependency_wait();
         dependency_met = true;
 #ifdef AYLA_B200_TRACE
-        if (stamps != nullptr && lane == 0 && prod_id == 0) stamps[14] = static_cast<long long>(global_timer_ns());
+        if (stamps != nullptr && lane == 0 && prod_id == 0) trace_stamp(stamps, 14);
 #endif
       }
       if (issuer && pf > 0 && prod_id == 0) {
@@ -664,7 +693,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
 #ifdef AYLA_B200_TRACE
         if (issuer && mine && stamps != nullptr && !first_issue_stamped && prod_id == 0) {
-          stamps[12] = static_cast<long long>(global_timer_ns());
+          trace_stamp(stamps, 12);
           first_issue_stamped = true;
         }
 #endif
@@ -713,7 +742,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (csk > 0 && p.inbox_in_ring) {
       // A cluster barrier counts every thread of the cluster: keep step with the one the
       // epilogue warps use before they send their partial tiles.
-      cluster_arrive();
+      cluster_arrive_relaxed();
       cluster_wait();
     }
   } else if (warp == 1) {
@@ -744,14 +773,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_full + stage * 8, phase, ST_TIMEOUT_FULL))
 #ifdef AYLA_B200_TRACE
           if (stamps != nullptr && lane == 0 && !first_operands_stamped) {
-            stamps[2] = static_cast<long long>(global_timer_ns());
+            trace_stamp(stamps, 2);
             first_operands_stamped = true;
           }
           if (stamps != nullptr && lane == 0 && first_unit_of_cta) {
             const int span = nkb, done = i;
             for (int qd = 1; qd <= 3; ++qd) {
               if (span >= 4 && done <= qd * span / 4 && qd * span / 4 < done + group) {
-                stamps[8 + qd] = static_cast<long long>(global_timer_ns());
+                trace_stamp(stamps, 8 + qd);
               }
             }
           }
@@ -825,7 +854,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
       AYLA_TRACE_END(1)
 #ifdef AYLA_B200_TRACE
-      if (stamps != nullptr && lane == 0) stamps[3] = static_cast<long long>(global_timer_ns());
+      if (stamps != nullptr && lane == 0) trace_stamp(stamps, 3);
       if (p.trace != nullptr && issuer) {
         p.trace[blockIdx.x * 16 + 12] = tr_fence;
         p.trace[blockIdx.x * 16 + 13] = tr_issue;
@@ -836,7 +865,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
     if (CG == 1 && csk > 0) cluster_wait();
     if (csk > 0 && p.inbox_in_ring) {
-      cluster_arrive();
+      cluster_arrive_relaxed();
       cluster_wait();
     }
   } else {
@@ -887,7 +916,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       AYLA_TRACE_WAIT(tr_wait, bw.wait(bar_acc_full + acc * 8, acc_phase, ST_TIMEOUT_ACC_FULL))
 #ifdef AYLA_B200_TRACE
       if (stamps != nullptr && warp == 2 && lane == 0 && !acc_seen_stamped) {
-        stamps[13] = static_cast<long long>(global_timer_ns());
+        trace_stamp(stamps, 13);
         acc_seen_stamped = true;
       }
 #endif
@@ -902,8 +931,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const int unit_groups = (unit_chunks + 1) / 2;
 
       // Hand the accumulator buffer back to the MMA warp (every warp arrives once per
-      // unit, after its last TMEM load has completed).
+      // unit, after its last TMEM load has completed).  The MMA warp waits for that only before
+      // the unit ACC_BUFS later: the last arrivals of a CTA would find nobody waiting, and for
+      // a CTA pair they would be remote arrivals still in flight when the leader leaves, so
+      // they are not sent.
+      static_assert(T::ACC_BUFS <= 2, "UnitCursor::follows looks at most two units ahead");
+      const bool release_awaited = cursor.follows(T::ACC_BUFS);
       auto release_accumulator = [&]() {
+        if (!release_awaited) return;
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -1029,13 +1064,22 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             *reinterpret_cast<uint4*>(my_store + lane * 128 + ((chunk16 ^ (lane & 7)) << 4)) =
                 make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
           }
+#ifdef AYLA_B200_TRACE
+          if (stamps != nullptr && warp == 2 && lane == 0 && c32 < 2) trace_stamp(stamps, 22 + c32);
+#endif
           if (half == 1) {
             fence_proxy_async_smem();
+#ifdef AYLA_B200_TRACE
+            if (stamps != nullptr && warp == 2 && lane == 0 && c32 < 2) trace_stamp(stamps, 24);
+#endif
             __syncwarp();
             if (lane == 0) {
               tma_store_3d(&tm_d, smem_u32(my_store), w.n0 + (c32 >> 1) * 64, w.m0 + q * 32, w.batch);
               tma_store_commit();
             }
+#ifdef AYLA_B200_TRACE
+            if (stamps != nullptr && warp == 2 && lane == 0 && c32 < 2) trace_stamp(stamps, 25);
+#endif
           }
         }
       };
@@ -1058,11 +1102,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const bool own_in_tmem = slice_cols >= CHUNK_COLS;
           if constexpr (CG == 1) cluster_wait();  // every CTA of the cluster has its inbox barrier ready
           if (p.inbox_in_ring) {
-            cluster_arrive();  // every CTA's MMAs are done: no ring is being read any more
+            // Every CTA's MMAs are done (its epilogue warps have seen the accumulator): no ring
+            // is being read any more.  The threads only meet here; nothing is published.
+            cluster_arrive_relaxed();
             cluster_wait();
           }
 #ifdef AYLA_B200_TRACE
-          if (stamps != nullptr && warp == 2 && lane == 0) stamps[6] = static_cast<long long>(global_timer_ns());
+          if (stamps != nullptr && warp == 2 && lane == 0) trace_stamp(stamps, 6);
 #endif
           auto send_chunk = [&](int c32, const uint32_t (&r)[32]) {
 #pragma unroll
@@ -1116,12 +1162,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
           }
 #ifdef AYLA_B200_TRACE
-          if (stamps != nullptr && warp == 2 && lane == 0) stamps[15] = static_cast<long long>(global_timer_ns());
+          if (stamps != nullptr && warp == 2 && lane == 0) trace_stamp(stamps, 15);
 #endif
           // The partials of this CTA's columns have all landed when the inbox barrier completes.
           bw.wait(bar_inbox, 0, ST_TIMEOUT_INBOX);
 #ifdef AYLA_B200_TRACE
-          if (stamps != nullptr && warp == 2 && lane == 0) stamps[7] = static_cast<long long>(global_timer_ns());
+          if (stamps != nullptr && warp == 2 && lane == 0) trace_stamp(stamps, 7);
 #endif
           const float4* mine = reinterpret_cast<const float4*>(smem + p.inbox_offset);
           const int row = w.m0 + row_in_tile;
@@ -1290,6 +1336,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll 1
             for (int g = wsub; g < unit_groups; g += 2) {
               tmem_ld_wait();
+#ifdef AYLA_B200_TRACE
+              if (stamps != nullptr && warp == 2 && lane == 0 && g == wsub) trace_stamp(stamps, 16);
+#endif
               issue(2 * g + 1, rb);
               consume(2 * g, ra);
               tmem_ld_wait();
@@ -1299,6 +1348,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 release_accumulator();
               }
               consume(2 * g + 1, rb);
+#ifdef AYLA_B200_TRACE
+              if (stamps != nullptr && warp == 2 && lane == 0 && (g >> 1) < 4) trace_stamp(stamps, 18 + (g >> 1));
+#endif
             }
           }
         } else {
@@ -1428,6 +1480,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         acc_phase ^= 1;
       }
     }
+#ifdef AYLA_B200_TRACE
+    if (stamps != nullptr && warp == 2 && lane == 0) trace_stamp(stamps, 17);
+#endif
     if constexpr (!T::TRANS_OUT) {
       // Shared memory must outlive the bulk stores that read it; their global writes are
       // complete, like every other store of the grid, when the grid is.
@@ -1436,7 +1491,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (warp == 2) {
       AYLA_TRACE_END(2)
 #ifdef AYLA_B200_TRACE
-      if (stamps != nullptr && lane == 0) stamps[4] = static_cast<long long>(global_timer_ns());
+      if (stamps != nullptr && lane == 0) trace_stamp(stamps, 4);
 #endif
     }
   }
@@ -1451,8 +1506,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   __syncthreads();
   if constexpr (CG == 2) {
     // The leader's MMAs write the peer's TMEM and both CTAs' barriers: neither
-    // CTA may free TMEM or exit before both are done.
-    cluster_arrive();
+    // CTA may free TMEM or exit before both are done.  Nothing is published by this meeting:
+    // every remote arrival a thread of either CTA sent has been waited for by its receiver, and
+    // the arrivals of the leader's commits on the peer's slot barriers precede the one on its
+    // accumulator barrier, which the peer's epilogue warps have seen.
+    cluster_arrive_relaxed();
     cluster_wait();
   }
   if (warp == 1) {
@@ -1460,7 +1518,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tmem_dealloc<CG>(tmem_base, T::TMEM_COLS);
   }
 #ifdef AYLA_B200_TRACE
-  if (stamps != nullptr && threadIdx.x == 32) stamps[5] = static_cast<long long>(global_timer_ns());
+  if (stamps != nullptr && threadIdx.x == 32) {
+    trace_stamp(stamps, 5);
+    long long* out = p.trace + 4096 + blockIdx.x * 64;
+    for (int i = 0; i < 40; ++i) out[i] = stamps[i];
+  }
 #endif
 #endif
 }

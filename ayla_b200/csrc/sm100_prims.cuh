@@ -60,6 +60,12 @@ __device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, float a, floa
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
+// The same without the release: the threads only meet, no write of theirs is published by it (a
+// release at cluster scope stalled each arriving warp for about half a microsecond).  Barriers that
+// were just initialised are published by fence.mbarrier_init.release.cluster instead.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -102,9 +108,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // Arrive on a barrier that may live in another CTA of the cluster.
+// Release at CTA scope only (the PTX default): what the arrival hands over here is TMEM, which
+// tcgen05.wait::ld and the tcgen05 fences order, not the memory model; a release at cluster scope
+// cost the arriving warp close to a microsecond.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // One poll of the barrier phase.  The plain form (the hardware parks the thread for its own

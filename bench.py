@@ -281,6 +281,141 @@ def run_case(args) -> None:
     print(f"{args.case}: {args.launches} {arm} launches of {op} {batch}x{m}x{n}x{k} done")
 
 
+STAMPS = {"entry": 0, "set-up done": 1, "preceding launch complete": 14, "first TMA issued": 12,
+          "first operands landed": 2, "last MMA committed": 3, "epilogue saw the accumulator": 13,
+          "first chunk in registers": 16, "first chunk staged": 22, "second chunk staged": 23,
+          "staging published (proxy fence)": 24, "first bulk store issued": 25,
+          "split-k: cluster met": 6, "split-k: own part sent": 15, "split-k: peers' parts in": 7,
+          "first 64-column group done": 18, "second 64-column group done": 19,
+          "last chunk handed to the stores": 17, "epilogue done": 4, "exit": 5}
+INTERVALS = (("entry", "set-up done"), ("preceding launch complete", "first TMA issued"),
+             ("preceding launch complete", "first operands landed"),
+             ("first operands landed", "last MMA committed"), ("last MMA committed", "epilogue saw the accumulator"),
+             ("last MMA committed", "first chunk in registers"),
+             ("last MMA committed", "first chunk staged"), ("last MMA committed", "second chunk staged"),
+             ("last MMA committed", "staging published (proxy fence)"),
+             ("last MMA committed", "first bulk store issued"),
+             ("last MMA committed", "split-k: cluster met"),
+             ("last MMA committed", "split-k: own part sent"), ("last MMA committed", "split-k: peers' parts in"),
+             ("last MMA committed", "first 64-column group done"),
+             ("last MMA committed", "second 64-column group done"),
+             ("last MMA committed", "last chunk handed to the stores"),
+             ("last MMA committed", "epilogue done"), ("last MMA committed", "exit"), ("entry", "exit"))
+
+
+def run_timeline(args) -> None:
+    """Where one launch spends its time: the per-CTA stamps of the trace build
+    (``python -m ayla_b200.build --trace``), read after a CUDA graph of ``--launches`` back-to-back
+    launches on operand sets rotating past L2 (the suite's regime).  Consecutive launches stamp into
+    two alternating buffers, so the last launch and the one before it are both kept.  Intervals
+    inside a CTA come from the SM's cycle counter, comparisons across CTAs from ``globaltimer``.
+    Only schedules without workspace slabs leave stamps (cluster k-splits do)."""
+    from ayla_b200 import build as _build
+
+    if "AYLA_B200_LIB" not in os.environ:
+        if not _build.TRACE_LIB_PATH.exists():
+            raise SystemExit("--timeline needs the trace build: python -m ayla_b200.build --trace")
+        os.environ["AYLA_B200_LIB"] = str(_build.TRACE_LIB_PATH)
+    from ayla_b200 import _lib
+    from ayla_b200.gemm_jit import select_gemm_schedule
+    from ayla_b200.suite import _copies
+
+    if args.case in CASES:
+        op, batch, m, n, k = CASES[args.case]
+    else:
+        op, dims = args.case.split(":")
+        values = [int(v) for v in dims.split(",")]
+        batch, (m, n, k) = (values[0], values[1:]) if op == "bmm" else (1, values)
+    if op == "swiglu":
+        raise SystemExit("--timeline covers mm, addmm and bmm")
+    dev = "cuda:0"
+    _lib.init(0)
+    td = torch.bfloat16 if args.dtype == "bfloat16" else torch.float16
+    schedule = json.loads(args.schedule) if args.schedule else dict(
+        select_gemm_schedule(op, args.dtype, m, n, k, batch).builder_config)
+    cfg = _lib.Config.from_dict(schedule)
+    if _lib.workspace_bytes(cfg, op, batch, m, n, k) > 0:
+        raise SystemExit("this schedule reduces through workspace slabs; the stamps need the workspace")
+    lead = (batch,) if op == "bmm" else ()
+    sets = []
+    for _ in range(_copies(2.0 * batch * (m * k + n * k + m * n))):
+        sets.append((torch.randn((*lead, m, k), device=dev).to(td),
+                     (torch.randn((*lead, n, k), device=dev) * k ** -0.5).to(td),
+                     torch.empty((*lead, m, n), device=dev, dtype=td)))
+    bias = torch.randn(n, device=dev).to(td)
+    sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+    words = 4096 + sm_count * 64
+    buffers = torch.zeros(2, words, dtype=torch.int64, device=dev)
+    stream = torch.cuda.Stream()
+
+    def launch(i: int) -> None:
+        a, bt, out = sets[i % len(sets)]
+        _lib.gemm(op, args.dtype, bias.data_ptr() if op == "addmm" else 0, a.data_ptr(), bt.data_ptr(),
+                  out.data_ptr(), batch, m, n, k, cfg, buffers[i % 2].data_ptr(), words * 8, 0, stream.cuda_stream)
+
+    with torch.cuda.stream(stream):
+        for i in range(3):
+            launch(i)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(args.launches):
+                launch(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(5):
+            buffers.zero_()
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+    per_launch_us = e0.elapsed_time(e1) * 1e3 / args.launches
+
+    def stamps_of(index: int) -> torch.Tensor:
+        rows = buffers[index % 2][4096:].view(sm_count, 64).cpu()
+        return rows[rows[:, STAMPS["exit"]] > 0].double()
+
+    last, before = stamps_of(args.launches - 1), stamps_of(args.launches - 2)
+    if last.numel() == 0:
+        raise SystemExit("no stamps: is AYLA_B200_LIB a trace build?")
+    entry_ns, exit_ns = last[:, 32], last[:, 33]
+    cycles = last[:, STAMPS["exit"]] - last[:, STAMPS["entry"]]
+    mhz = float((cycles / (exit_ns - entry_ns)).median() * 1e3)
+
+    def on_shared_clock(rows: torch.Tensor, name: str) -> torch.Tensor:
+        """ns on the time base all SMs share: the CTA's entry time plus its cycles since entry."""
+        return rows[:, 32] + (rows[:, STAMPS[name]] - rows[:, STAMPS["entry"]]) * 1e3 / mhz
+
+    print(f"{args.case}: {op} {batch}x{m}x{n}x{k} {args.dtype}, schedule {json.dumps(schedule)}")
+    print(f"{per_launch_us:.2f} us per launch over {args.launches} back-to-back launches in a graph (trace build); "
+          f"{last.shape[0]} CTAs; SM clock {mhz:.0f} MHz from the stamps")
+    print("per-CTA intervals of the last launch, us at that clock from the SM cycle counter (min / median / max over CTAs):")
+    for first, second in INTERVALS:
+        a, b = last[:, STAMPS[first]], last[:, STAMPS[second]]
+        ok = (a > 0) & (b > 0)
+        if ok.any():
+            d = (b[ok] - a[ok]) / mhz
+            print(f"  {first:28s} -> {second:32s} {d.min():7.2f} / {d.median():7.2f} / {d.max():7.2f}")
+    print("across CTAs, us (globaltimer at entry and exit, steps of 0.26 us on this GPU, cycles in between):")
+    print(f"  first entry -> last exit: {(exit_ns.max() - entry_ns.min()) / 1e3:.2f}; entries spread over "
+          f"{(entry_ns.max() - entry_ns.min()) / 1e3:.2f}, exits over {(exit_ns.max() - exit_ns.min()) / 1e3:.2f}")
+    if before.numel():
+        ready = on_shared_clock(last, "preceding launch complete")[last[:, STAMPS["preceding launch complete"]] > 0]
+        prev_exit = before[:, 33].max()
+        print(f"  last exit of the launch before -> this launch's producers released: "
+              f"{(ready.min() - prev_exit) / 1e3:.2f} (first) / {(ready.median() - prev_exit) / 1e3:.2f} (median); "
+              f"last exit to last exit {(exit_ns.max() - prev_exit) / 1e3:.2f}")
+
+
+def _sm_clock_mhz() -> str:
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(0)
+        return str(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+    except Exception:
+        return "unknown"
+
+
 def hbm_rows(peaks: dict) -> list[dict]:
     """Weight-streaming shapes (HBM-bound: the weight is read once per launch): graph replay with
     operand sets rotating through more than 2.5x L2, cuBLAS interleaved (``ayla_b200.suite``)."""
@@ -441,6 +576,8 @@ def main() -> None:
     parser.add_argument("--schedule", default=None, help="JSON schedule for --case (default: the table's)")
     parser.add_argument("--dtype", default="bfloat16")
     parser.add_argument("--torch", action="store_true", help="--case launches the cuBLAS counterpart instead")
+    parser.add_argument("--timeline", action="store_true",
+                        help="--case prints the per-CTA stage times of a launch (needs the trace build)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -451,7 +588,7 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path "
                          "(use --impl reference for the CPU baseline)")
     if args.case:
-        run_case(args)
+        run_timeline(args) if args.timeline else run_case(args)
         return
 
     # Only the JSON line may reach stdout: libraries that write there from native code (NCCL prints its
