@@ -516,7 +516,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // issued, 12 first TMA load issued, 13 epilogue saw the first finished accumulator, 14 the preceding
   // launch is complete (dependency wait returned), 15 split-k parts sent, 16 first accumulator chunk in
   // registers, 17 last output chunk handed to the store path, 18-21 the first warp's 64-column groups done,
-  // 22/23 its first two chunks staged, 24 staging published to the async proxy, 25 bulk store issued.
+  // 22/23 its first two chunks staged, 24 staging published to the async proxy, 25 bulk store issued,
+  // 26 split-k: own partial of the first chunk in registers, 27 that chunk summed.
   long long* stamps = (p.trace != nullptr) ? reinterpret_cast<long long*>(smem_misc + T::MISC_BYTES) : nullptr;
   if (stamps != nullptr && threadIdx.x == 0) {
     for (int i = 0; i < 40; ++i) stamps[i] = 0;
@@ -1174,78 +1175,87 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (own_in_tmem) {
             // Sum, in split order, the partials of this CTA's columns: its own from TMEM,
             // the others from the exchange area.  `lc` counts 32-column chunks of the slice.
+            // All eight loads of a peer's partial are issued before any is added (summing element
+            // by element inside the loop over the splits left every load's latency exposed: 0.8 us
+            // per chunk measured).
             auto reduce_chunk = [&](int lc, const uint32_t (&own)[32], float (&v)[32]) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int s = 0; s < csk; ++s) {
-                  float4 x;
-                  if (s == csk_rank) {
-                    x = make_float4(__uint_as_float(own[4 * j]), __uint_as_float(own[4 * j + 1]),
-                                    __uint_as_float(own[4 * j + 2]), __uint_as_float(own[4 * j + 3]));
-                  } else {
-                    x = mine[((s > csk_rank ? s - 1 : s) * slice_c4 + lc * 8 + j) * 128 + row_in_tile];
+              for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+#pragma unroll 1
+              for (int s = 0; s < csk; ++s) {
+                if (s == csk_rank) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(own[j]);
+                } else {
+                  const float4* src = mine + ((s > csk_rank ? s - 1 : s) * slice_c4 + lc * 8) * 128 + row_in_tile;
+                  float4 x[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) x[j] = src[j * 128];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    v[4 * j + 0] += x[j].x;
+                    v[4 * j + 1] += x[j].y;
+                    v[4 * j + 2] += x[j].z;
+                    v[4 * j + 3] += x[j].w;
                   }
-                  sum.x += x.x;
-                  sum.y += x.y;
-                  sum.z += x.z;
-                  sum.w += x.w;
                 }
-                v[4 * j + 0] = sum.x;
-                v[4 * j + 1] = sum.y;
-                v[4 * j + 2] = sum.z;
-                v[4 * j + 3] = sum.w;
               }
             };
             const int first_c32 = (csk_rank << slice_shift) >> 5;  // tile chunk index of the slice
             const int slice_chunks = slice_cols >> 5;
             if constexpr (CHUNK_COLS == 32) {
-              if (!T::TRANS_OUT && slice_cols >= 64) {
-                // Whole 64-column groups: through the staging rows and a bulk store, like
-                // the ordinary epilogue.
 #pragma unroll 1
-                for (int g = wsub; 2 * g < slice_chunks; g += 2) {
-                  uint32_t ra[32], rb[32];
-                  tmem_ld_32x32(t_acc + (first_c32 + 2 * g) * 32, ra);
-                  tmem_ld_32x32(t_acc + (first_c32 + 2 * g + 1) * 32, rb);
-                  tmem_ld_wait();
-                  const bool live = rows_live && (w.n0 + ((first_c32 + 2 * g) >> 1) * 64) < p.n;
-                  float v[32];
-                  reduce_chunk(2 * g, ra, v);
-                  if (live) finish_chunk(v, first_c32 + 2 * g);
-                  reduce_chunk(2 * g + 1, rb, v);
-                  if (live) finish_chunk(v, first_c32 + 2 * g + 1);
-                }
-              } else {
-#pragma unroll 1
-                for (int lc = wsub; lc < slice_chunks; lc += 2) {
-                  const int c32 = first_c32 + lc;
-                  uint32_t ra[32];
-                  tmem_ld_32x32(t_acc + c32 * 32, ra);
-                  tmem_ld_wait();
-                  float v[32];
-                  reduce_chunk(lc, ra, v);
-                  const int col0 = w.n0 + c32 * 32;
-                  if (!(rows_live && col0 < p.n)) continue;
-                  if constexpr (T::TRANS_OUT) {
-                    finish_chunk(v, c32);
-                  } else if (row < row_end) {
-                    // A lone 32-column chunk: 64 contiguous bytes of this thread's output row.
-                    if constexpr (T::EPI == EPI_BIAS) {
+              for (int lc = wsub; lc < slice_chunks; lc += 2) {
+                const int c32 = first_c32 + lc;
+                uint32_t ra[32];
+                tmem_ld_32x32(t_acc + c32 * 32, ra);
+                tmem_ld_wait();
+#ifdef AYLA_B200_TRACE
+                if (stamps != nullptr && warp == 2 && lane == 0 && lc == wsub) trace_stamp(stamps, 26);
+#endif
+                float v[32];
+                reduce_chunk(lc, ra, v);
+#ifdef AYLA_B200_TRACE
+                if (stamps != nullptr && warp == 2 && lane == 0 && lc == wsub) trace_stamp(stamps, 27);
+#endif
+                const int col0 = w.n0 + c32 * 32;
+                if (!(rows_live && col0 < p.n)) continue;
+                if constexpr (T::TRANS_OUT) {
+                  finish_chunk(v, c32);
+                } else if (row < row_end) {
+                  // A lone 32-column chunk: 64 contiguous bytes of this thread's output row.
+                  if constexpr (T::EPI == EPI_BIAS) {
 #pragma unroll
-                      for (int j = 0; j < 32; ++j) v[j] += smem_bias[bias_buf * BN + c32 * 32 + j];
-                    }
-                    apply_act_chunk<32>(v, act);
-                    gate_chunk(v, c32);
-                    uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) +
-                                   2 * (w.batch * p.out_batch_stride + static_cast<long long>(row) * p.out_ld + col0);
+                    for (int j = 0; j < 32; ++j) v[j] += smem_bias[bias_buf * BN + c32 * 32 + j];
+                  }
+                  apply_act_chunk<32>(v, act);
+                  gate_chunk(v, c32);
+                }
+                // Through this warp's staging rows, so that one store instruction writes eight
+                // rows of 64 contiguous bytes instead of 16 bytes of each of 32 rows (the load/store
+                // unit takes a cycle per 128-byte line touched: 0.6 us for the tile the direct way).
+                // Row r holds its four 16-byte pieces at r * 64, piece c at position c ^ ((r >> 1) & 3).
+                if constexpr (!T::TRANS_OUT) {
+                  __syncwarp();
+                  if (row < row_end) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                      if (col0 + 8 * j < p.n) {
-                        *reinterpret_cast<uint4*>(dst + 16 * j) =
-                            make_uint4(pack2(v[8 * j], v[8 * j + 1], is_bf16), pack2(v[8 * j + 2], v[8 * j + 3], is_bf16),
-                                       pack2(v[8 * j + 4], v[8 * j + 5], is_bf16), pack2(v[8 * j + 6], v[8 * j + 7], is_bf16));
-                      }
+                      *reinterpret_cast<uint4*>(my_store + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                          make_uint4(pack2(v[8 * j], v[8 * j + 1], is_bf16), pack2(v[8 * j + 2], v[8 * j + 3], is_bf16),
+                                     pack2(v[8 * j + 4], v[8 * j + 5], is_bf16), pack2(v[8 * j + 6], v[8 * j + 7], is_bf16));
+                    }
+                  }
+                  __syncwarp();
+                  const int piece = lane & 3;
+                  const int col = col0 + piece * 8;
+                  uint8_t* dst0 = reinterpret_cast<uint8_t*>(p.out) + 2 * (w.batch * p.out_batch_stride + col);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const int r = i * 8 + (lane >> 2);
+                    const int out_row = w.m0 + q * 32 + r;
+                    const uint4 x = *reinterpret_cast<const uint4*>(my_store + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4));
+                    if (out_row < row_end && col < p.n) {
+                      *reinterpret_cast<uint4*>(dst0 + 2 * static_cast<long long>(out_row) * p.out_ld) = x;
                     }
                   }
                 }

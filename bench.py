@@ -286,6 +286,7 @@ STAMPS = {"entry": 0, "set-up done": 1, "preceding launch complete": 14, "first 
           "first chunk in registers": 16, "first chunk staged": 22, "second chunk staged": 23,
           "staging published (proxy fence)": 24, "first bulk store issued": 25,
           "split-k: cluster met": 6, "split-k: own part sent": 15, "split-k: peers' parts in": 7,
+          "split-k: own partial in registers": 26, "split-k: first chunk summed": 27, 
           "first 64-column group done": 18, "second 64-column group done": 19,
           "last chunk handed to the stores": 17, "epilogue done": 4, "exit": 5}
 INTERVALS = (("entry", "set-up done"), ("preceding launch complete", "first TMA issued"),
@@ -297,6 +298,8 @@ INTERVALS = (("entry", "set-up done"), ("preceding launch complete", "first TMA 
              ("last MMA committed", "first bulk store issued"),
              ("last MMA committed", "split-k: cluster met"),
              ("last MMA committed", "split-k: own part sent"), ("last MMA committed", "split-k: peers' parts in"),
+             ("last MMA committed", "split-k: own partial in registers"),
+             ("last MMA committed", "split-k: first chunk summed"),
              ("last MMA committed", "first 64-column group done"),
              ("last MMA committed", "second 64-column group done"),
              ("last MMA committed", "last chunk handed to the stores"),
