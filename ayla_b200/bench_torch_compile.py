@@ -170,6 +170,28 @@ def gated_pair_entry(tokens: int = 8, hidden: int = 6656, attn: int = 4096):
             (lambda h, v, w_gate, w_o: (torch.sigmoid(h @ w_gate.t()) * v) @ w_o.t()), (h, v, w_gate, w_o))
 
 
+def rmsnorm_projection_entry(tokens: int = 4096, hidden: int = 4096, out_features: int = 6144):
+    """An RMSNorm followed by a projection (a decoder block's pre-norm and fused QKV projection) as
+    a module whose weights Inductor's freezing turns into constants: routed, the norm weight is
+    folded into the projection weight at compile time and the row factors are applied in the GEMM's
+    epilogue (``jit_mm_rowmul``), so the normalised activations never exist in memory."""
+
+    class NormThenProject(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.g = torch.nn.Parameter(1.0 + 0.1 * torch.randn(hidden))
+            self.w = torch.nn.Parameter(torch.randn(out_features, hidden) * hidden ** -0.5)
+
+        def forward(self, x):
+            return F.linear(F.rms_norm(x, (hidden,), self.g, 1e-5), self.w)
+
+    torch.manual_seed(3)
+    block = NormThenProject().to(device="cuda", dtype=torch.bfloat16).eval()
+    x = torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16)
+    return (f"RMSNorm + projection, frozen weights, {tokens} tokens ({hidden} -> {out_features})", block, (x,),
+            {"freezing": True})
+
+
 def gated_block_fn(attn: int, ffn: int, kv: int):
     """The block body as a function of its activations and weights (see ``gated_block_entry``)."""
 
@@ -236,8 +258,10 @@ def _time_callable(fn, args, rounds: int = 7, launches: int = 4) -> float:
     return statistics.median(samples)
 
 
-def run_corpus_entry(name: str, fn, args) -> dict:
-    """The reference driver's three rows for one entry."""
+def run_corpus_entry(name: str, fn, args, options: dict | None = None) -> dict:
+    """The reference driver's three rows for one entry; ``options`` are Inductor settings both
+    compiled arms run under (``{"freezing": True}`` for an entry whose weights are module parameters)."""
+    options = dict(options or {})
     from torch._inductor.utils import run_and_get_code
 
     def first(result):
@@ -252,10 +276,12 @@ def run_corpus_entry(name: str, fn, args) -> dict:
         if routed:
             routing.install()
         try:
-            with torch.no_grad(), inductor_config.patch(force_disable_caches=True):
-                # Two lambdas, not one: Dynamo caches on the code object.
-                compiled = torch.compile((lambda *a: fn(*a)) if routed else (lambda *b: fn(*b)), fullgraph=True,
-                                         dynamic=False)
+            with torch.no_grad(), inductor_config.patch(force_disable_caches=True, **options):
+                # Two lambdas, not one: Dynamo caches on the code object.  A module is compiled as
+                # itself, so that freezing finds its parameters.
+                target = fn if isinstance(fn, torch.nn.Module) else (
+                    (lambda *a: fn(*a)) if routed else (lambda *b: fn(*b)))
+                compiled = torch.compile(target, fullgraph=True, dynamic=False)
                 _, code = run_and_get_code(compiled, *args)
                 row[f"{arm}_ms"] = _time_callable(compiled, args)
                 got = first(compiled(*args)).float()
@@ -267,17 +293,19 @@ def run_corpus_entry(name: str, fn, args) -> dict:
             text = "\n".join(code)
             row["routed_calls_in_generated_code"] = {
                 op: text.count(f"torch.ops.ayla.{op}") for op in
-                ("jit_mm_bf16_fn", "jit_mm_sigmoid_bf16_fn", "jit_mm_sigmoid_mul_bf16_fn", "swiglu_bf16_fn")}
+                ("jit_mm_bf16_fn", "jit_mm_sigmoid_bf16_fn", "jit_mm_sigmoid_mul_bf16_fn", "jit_mm_rowmul_bf16_fn",
+                 "swiglu_bf16_fn")}
             row["triton_matmuls_left"] = text.count("triton_tem_") + text.count("extern_kernels.mm(")
     row["speedup_vs_stock_inductor"] = row["compiled_ms"] / row["ayla_compiled_ms"]
     return row
 
 
 def run_corpus(token_counts) -> list[dict]:
-    entries = [gemm_sigmoid_entry(), gated_pair_entry()] + [gated_block_entry(t) for t in token_counts]
+    entries = ([gemm_sigmoid_entry(), gated_pair_entry(), rmsnorm_projection_entry()]
+               + [gated_block_entry(t) for t in token_counts])
     rows = []
-    for name, fn, args in entries:
-        rows.append(run_corpus_entry(name, fn, args))
+    for name, fn, args, *options in entries:
+        rows.append(run_corpus_entry(name, fn, args, *options))
         print(json.dumps(rows[-1]), flush=True)
         del fn, args
         torch.cuda.empty_cache()

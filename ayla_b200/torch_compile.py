@@ -35,14 +35,15 @@ _DTYPE_NAMES = {torch.float16: "float16", torch.bfloat16: "bfloat16"}
 def gemm_fn_op(operation: str, dtype: str, namespace: str = DEFAULT_NAMESPACE,
                activation: str = "none", gated: bool = False) -> torch._ops.OpOverload:
     """Functional form ``(bias?, a, bt[, mul]) -> out`` of ``gemm_op`` / ``gemm_act_op`` /
-    ``gemm_act_mul_op`` (the result is allocated by the op), the form a functional FX graph can
-    hold.  Counterpart of the reference's allocating ops (ayla/gemm_collection/dynamic_m.py:90-121).
+    ``gemm_act_mul_op`` / (``gated="row"``) ``gemm_act_rowmul_op`` (the result is allocated by the
+    op), the form a functional FX graph can hold.  Counterpart of the reference's allocating ops (ayla/gemm_collection/dynamic_m.py:90-121).
     Cached: one op per distinct argument tuple, however the defaults were spelled."""
-    return _gemm_fn_op(operation, dtype, namespace, activation, bool(gated))
+    return _gemm_fn_op(operation, dtype, namespace, activation, gated if gated == "row" else bool(gated))
 
 
 @cache
-def _gemm_fn_op(operation: str, dtype: str, namespace: str, activation: str, gated: bool) -> torch._ops.OpOverload:
+def _gemm_fn_op(operation: str, dtype: str, namespace: str, activation: str,
+                gated: bool | str) -> torch._ops.OpOverload:
     compiler = gemm_jit_compiler(operation, dtype, activation, gated)
 
     def infer(*inputs: torch.Tensor):
@@ -512,6 +513,108 @@ def route_swiglu_concat(graph: torch.fx.Graph) -> int:
     return rewritten
 
 
+def _constant_tensor(node, module) -> torch.Tensor | None:
+    """The tensor a node denotes when it is a constant of the graph's module (a parameter that
+    Inductor's freezing turned into an attribute), seen through ``permute``/``t`` views."""
+    if not isinstance(node, torch.fx.Node):
+        return None
+    if node.op == "get_attr":
+        value = module
+        for part in str(node.target).split("."):
+            value = getattr(value, part, None)
+        return value if isinstance(value, torch.Tensor) else None
+    if _is_call(node, aten.permute.default):
+        inner = _constant_tensor(node.args[0], module)
+        return None if inner is None else inner.permute(list(node.args[1]))
+    if _is_call(node, aten.t.default):
+        inner = _constant_tensor(node.args[0], module)
+        return None if inner is None else inner.t()
+    return None
+
+
+def _rms_norm_source(node):
+    """If ``node`` is ``x * rsqrt(mean(x^2, -1, keepdim) + eps) * g`` computed in fp32 and rounded to
+    the type of ``x`` (the decomposition of ``rms_norm`` with a weight), return ``(x, rsqrt node, g)``."""
+    val = _val(node)
+    product = _strip_convert(node, val.dtype if val is not None else None)
+    if not _is_call(product, aten.mul.Tensor) or len(product.args) != 2:
+        return None
+    for scaled, g in (product.args, product.args[::-1]):
+        if not _is_call(scaled, aten.mul.Tensor) or len(scaled.args) != 2 or not isinstance(g, torch.fx.Node):
+            continue
+        for xf, r in (scaled.args, scaled.args[::-1]):
+            if not _is_call(r, aten.rsqrt.default) or not isinstance(xf, torch.fx.Node):
+                continue
+            shifted = r.args[0]
+            if not ((_is_call(shifted, aten.add.Scalar) or _is_call(shifted, aten.add.Tensor))
+                    and isinstance(shifted.args[1], (int, float))):
+                continue
+            mean = shifted.args[0]
+            xv = _val(xf)
+            if not _is_call(mean, aten.mean.dim) or xv is None or xv.dtype != torch.float32:
+                continue
+            dims, keepdim = list(mean.args[1]), (mean.args[2] if len(mean.args) > 2 else False)
+            if dims not in ([-1], [xv.dim() - 1]) or not keepdim:
+                continue
+            square = mean.args[0]
+            squared = ((_is_call(square, aten.pow.Tensor_Scalar) and square.args[0] is xf and square.args[1] == 2)
+                       or (_is_call(square, aten.mul.Tensor) and square.args[0] is xf and square.args[1] is xf))
+            if not squared:
+                continue
+            x = _strip_convert(xf, torch.float32)
+            if x is xf or val is None or _val(x) is None or _val(x).dtype != val.dtype:
+                continue
+            return x, r, g
+    return None
+
+
+def route_rmsnorm(graph: torch.fx.Graph) -> int:
+    """Rewrite ``rms_norm(x, weight=g) @ W.T`` with constant ``g`` and ``W`` (Inductor freezing) into
+    ``r * (x @ (W * g).T)``: ``g`` is folded into the projection weight once, here, and the per-row
+    factor ``r = rsqrt(mean(x^2) + eps)`` multiplies the fp32 accumulator in the GEMM's epilogue
+    (``gemm_act_rowmul_op``), so the normalised activations are neither written nor read back.  With
+    weights that are graph inputs (no freezing) nothing is constant and the pattern is left alone."""
+    module = graph.owning_module
+    if module is None:
+        return 0
+    from .rmsnorm_linear import fold_norm_weight
+
+    rewritten = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten.mm.default) or len(node.args) != 2:
+            continue
+        lhs, rhs = node.args
+        found = _rms_norm_source(lhs) if isinstance(lhs, torch.fx.Node) else None
+        if found is None:
+            continue
+        x, r, g = found
+        claim = _claim("mm", x, rhs)  # x has the shape, type and layout of the normalised activations
+        g_const, w_const = _constant_tensor(g, module), _constant_tensor(rhs, module)
+        rv = _val(rhs)
+        if claim is None or g_const is None or w_const is None or rv is None:
+            continue
+        dtype, (m, n, k) = claim
+        if tuple(w_const.shape) != (k, n) or tuple(g_const.shape) != (k,):
+            continue
+        name = f"_ayla_b200_folded_weight{rewritten}"
+        while hasattr(module, name):
+            name += "_"
+        module.register_buffer(name, fold_norm_weight(w_const.t(), g_const).contiguous(), persistent=False)
+        with graph.inserting_before(node):
+            weight = graph.get_attr(name)
+            weight.meta["val"] = rv.t().contiguous()
+            factors = graph.call_function(prims.convert_element_type.default, (r, _TORCH_DTYPES[dtype]))
+            factors.meta["val"] = _val(r).to(_TORCH_DTYPES[dtype])
+            new = graph.call_function(gemm_fn_op("mm", dtype, DEFAULT_NAMESPACE, "none", "row"), (x, weight, factors))
+            new.meta.update({key: v for key, v in node.meta.items() if key != "original_aten"})
+        node.replace_all_uses_with(new)
+        graph.erase_node(node)
+        rewritten += 1
+    if rewritten:
+        graph.eliminate_dead_code()
+    return rewritten
+
+
 def route_gemms(graph: torch.fx.Graph) -> int:
     """Rewrite every claimed ``aten.mm/addmm/bmm`` node of ``graph``; returns how many."""
     rewritten = 0
@@ -559,6 +662,7 @@ class AylaRoutingPass(CustomGraphPass):
     def __call__(self, graph: torch.fx.Graph) -> None:
         route_swiglu(graph)  # first: it consumes two mm nodes route_gemms would claim
         route_swiglu_concat(graph)
+        route_rmsnorm(graph)
         route_gated(graph)
         route_activations(graph)
         route_gemms(graph)
@@ -584,6 +688,7 @@ def emittable_ops() -> list[tuple]:
             for activation in ACTIVATIONS:
                 ops.append((operation, dtype, DEFAULT_NAMESPACE, activation, False))
                 ops.append((operation, dtype, DEFAULT_NAMESPACE, activation, True))
+        ops.append(("mm", dtype, DEFAULT_NAMESPACE, "none", "row"))
     return ops
 
 

@@ -241,6 +241,66 @@ def test_gated_decoder_block_body_is_routed_completely():
     assert found.count(torch.ops.ayla.jit_mm_bf16_fn.default) == 3
 
 
+def _freeze(gm, constants):
+    """Turn placeholders into attributes of the module, as Inductor's freezing does with parameters."""
+    for node in list(gm.graph.nodes):
+        if node.op == "placeholder" and node.target in constants:
+            gm.register_buffer(f"_frozen_{node.target}", constants[node.target], persistent=False)
+            with gm.graph.inserting_before(node):
+                attr = gm.graph.get_attr(f"_frozen_{node.target}")
+                attr.meta.update(node.meta)
+            node.replace_all_uses_with(attr)
+            gm.graph.erase_node(node)
+    gm.recompile()
+    return gm
+
+
+def rms_then_project(x, g, w):
+    return torch.mm(torch.nn.functional.rms_norm(x, (x.shape[-1],), g, 1e-5), w.t())
+
+
+def test_rmsnorm_before_a_projection_with_constant_weights_becomes_a_row_scaled_gemm():
+    m, n, k = 64, 256, 128
+    gm = trace(rms_then_project, ((m, k), BF16, "cuda"), ((k,), BF16, "cuda"), ((n, k), BF16, "cuda"))
+    names = [node.target for node in gm.graph.nodes if node.op == "placeholder"]
+    torch.manual_seed(0)
+    g, w = torch.randn(k).to(BF16), torch.randn(n, k).to(BF16)
+    _freeze(gm, {names[1]: g, names[2]: w})
+    assert tc.route_rmsnorm(gm.graph) == 1
+    gm.graph.lint()
+    assert torch.ops.ayla.jit_mm_rowmul_bf16_fn.default in targets(gm) and aten.mm.default not in targets(gm)
+    call = next(node for node in gm.graph.nodes if node.target is torch.ops.ayla.jit_mm_rowmul_bf16_fn.default)
+    x_node, weight_node, factors_node = call.args
+    assert x_node.op == "placeholder" and weight_node.op == "get_attr"
+    folded = getattr(gm, weight_node.target)
+    assert folded.shape == (n, k) and folded.is_contiguous() and folded.dtype == BF16
+    assert torch.equal(folded, (w.float() * g.float()).to(BF16))
+    assert factors_node.meta["val"].shape == (m, 1) and factors_node.meta["val"].dtype == BF16
+    # the normalised activations are no longer computed: only the row reduction is left
+    assert sum(1 for t in targets(gm) if t is aten.mul.Tensor) == 0
+    # and the rewrite is the same function: r * (x @ (W * g).T) against rms_norm(x, g) @ W.T
+    x = torch.randn(m, k).to(BF16)
+    want = rms_then_project(x.float(), g.float(), w.float())
+    r = torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5).to(BF16).float()
+    got = r * (x.float() @ folded.float().t())
+    assert (got - want).norm() / want.norm() < 5e-3
+
+
+def test_rmsnorm_routing_needs_constant_weights_and_the_exact_pattern():
+    m, n, k = 64, 256, 128
+    specs = (((m, k), BF16, "cuda"), ((k,), BF16, "cuda"), ((n, k), BF16, "cuda"))
+    gm = trace(rms_then_project, *specs)  # weights are graph inputs: nothing to fold
+    assert tc.route_rmsnorm(gm.graph) == 0
+    # a norm over another axis is not RMSNorm over the features
+    def other_axis(x, g, w):
+        xf = x.float()
+        return torch.mm((xf * torch.rsqrt(xf.pow(2).mean(0, keepdim=True) + 1e-5) * g).to(x.dtype), w.t())
+    gm = trace(other_axis, *specs)
+    names = [node.target for node in gm.graph.nodes if node.op == "placeholder"]
+    _freeze(gm, {names[1]: torch.randn(k).to(BF16), names[2]: torch.randn(n, k).to(BF16)})
+    assert tc.route_rmsnorm(gm.graph) == 0
+
+
 def test_every_op_the_pass_can_emit_is_registered_by_install():
     """On a hit in Inductor's code cache the pass never runs in the new process: the cached code
     names torch.ops.ayla.* ops, which must exist after install() alone."""
@@ -256,6 +316,7 @@ def test_every_op_the_pass_can_emit_is_registered_by_install():
                     for gated in (False, True):
                         name = f"{_op_name(operation, dtype, activation, gated)}_fn"
                         assert hasattr(torch.ops.ayla, name), name
+            assert hasattr(torch.ops.ayla, f"jit_mm_rowmul_{short}_fn")
         # every activation the matcher can name is one of those
         assert {"relu", "sigmoid", "silu", "gelu", "gelu_tanh"} <= set(ACTIVATIONS)
     finally:
@@ -386,6 +447,33 @@ def test_torch_compile_fuses_a_gated_projection(ayla_installed):
     torch.testing.assert_close(actual, expected, atol=0.06, rtol=0.03)
     assert any("jit_mm_sigmoid_mul_bf16" in source for source in code)
     assert any("jit_mm_bf16" in source for source in code)
+
+
+@pytest.mark.gpu
+def test_torch_compile_routes_rmsnorm_before_a_projection_when_the_weights_are_frozen(ayla_installed):
+    """With Inductor's freezing the norm weight and the projection weight are constants: the norm
+    weight is folded into the projection, the row factor goes into the GEMM's epilogue."""
+    from torch._inductor.utils import run_and_get_code
+
+    class NormThenProject(torch.nn.Module):
+        def __init__(self, hidden, out_features):
+            super().__init__()
+            self.g = torch.nn.Parameter(1.0 + 0.1 * torch.randn(hidden))
+            self.w = torch.nn.Parameter(torch.randn(out_features, hidden) * hidden ** -0.5)
+
+        def forward(self, x):
+            return torch.nn.functional.linear(torch.nn.functional.rms_norm(x, (x.shape[-1],), self.g, 1e-5), self.w)
+
+    torch.manual_seed(0)
+    block = NormThenProject(512, 768).to(device="cuda", dtype=torch.bfloat16).eval()
+    x = torch.randn(200, 512, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        expected = block(x)
+        with inductor_config.patch(force_disable_caches=True, freezing=True):
+            actual, code = run_and_get_code(torch.compile(block, fullgraph=True, dynamic=False), x)
+    assert any("jit_mm_rowmul_bf16" in source for source in code)
+    error = (actual.float() - expected.float()).norm() / expected.float().norm()
+    assert error < 5e-3, error
 
 
 @pytest.mark.gpu
