@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 from pathlib import Path
 
@@ -112,7 +113,12 @@ def candidates(op: str, batch: int, m: int, n: int, k: int) -> list[dict]:
     return out
 
 
-def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: int = 5, light: bool = False) -> dict:
+def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: int = 5, light: bool = False,
+               only: list[dict] | None = None) -> dict:
+    """Rank schedules for one shape next to cuBLAS.  With ``only`` (a play-off between the winners of
+    earlier sweeps) just those schedules are timed, twice -- on the GPU as it is and again right after
+    a third of a second of dense GEMMs, when the SM clock sits under the power cap -- and ranked by the
+    product of the two times: the weight-streaming schedules rank differently in the two states."""
     dev = "cuda"
     td = torch.bfloat16 if dtype == "bfloat16" else torch.float16
     lead = (batch,) if op == "bmm" else ()
@@ -131,7 +137,7 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
     workspace = torch.zeros(16, dtype=torch.uint8, device=dev)
     fns = {}
     configs = {}
-    for i, cand in enumerate(candidates(op, batch, m, n, k)):
+    for i, cand in enumerate(only if only is not None else candidates(op, batch, m, n, k)):
         cfg = _lib.Config.from_dict(cand)
         if not _lib.config_valid(cfg, op, dtype, batch, m, n, k):
             continue
@@ -166,12 +172,27 @@ def tune_shape(op: str, dtype: str, batch: int, m: int, n: int, k: int, rounds: 
 
     fns["torch"] = cublas
     times = time_interleaved(fns, launches, rounds)
+    if only is not None and len(fns) > 1:
+        heater = torch.randn(8192, 8192, device=dev).to(torch.bfloat16)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(400):  # about 0.7 ms each: stop after a third of a second
+            torch.mm(heater, heater)
+            stop.record()
+            if stop.query() and start.elapsed_time(stop) > 330.0:
+                break
+        torch.cuda.synchronize()
+        del heater
+        hot = time_interleaved(fns, launches, rounds)
+        times = {name: math.sqrt(ms * hot[name]) for name, ms in times.items()}
     torch_ms = times.pop("torch")
     ranked = sorted(times.items(), key=lambda kv: kv[1])
-    if not ranked:
+    if not ranked or only is not None:
         del sets
         torch.cuda.empty_cache()
-        return dict(op=op, dtype=dtype, batch=batch, m=m, n=n, k=k, torch_us=torch_ms * 1e3, results=[])
+        results = [dict(config=configs[name], us=ms * 1e3, tflops=flops / ms / 1e9, gbs=nbytes / ms / 1e6,
+                        percentage_of_torch=100.0 * torch_ms / ms) for name, ms in ranked]
+        return dict(op=op, dtype=dtype, batch=batch, m=m, n=n, k=k, torch_us=torch_ms * 1e3, results=results)
 
     def refine_pass(tweaks_for, label):
         """Time variations of the two fastest schedules next to the fastest itself (the yardstick that
@@ -343,6 +364,34 @@ def measure_isolated(shapes, out_path: Path, shapes_file: Path, rounds: int = 3,
         print(f"[autotune] {stuck}: {reason}; restarting the worker", flush=True)
 
 
+def playoff(results_paths: list[Path], out_path: Path, keep: int = 3, rounds: int = 5) -> None:
+    """Time the ``keep`` fastest schedules of every results file against each other, shape by shape in
+    the first file's order, and write the ranking to ``out_path`` (same format, resumable): two sweeps
+    of the same shape, run at different times, rank close schedules differently, and their own times
+    cannot be compared across runs."""
+    _lib.init(torch.cuda.current_device())
+    sweeps = [_load_done(path) for path in results_paths]
+    done = _load_done(out_path)
+    for shape in sweeps[0]:
+        if shape in done:
+            continue
+        seeds: list[dict] = []
+        for sweep in sweeps:
+            for entry in sweep.get(shape, {}).get("results", [])[:keep]:
+                cand = {key: value for key, value in entry["config"].items() if key != "sustained_us"}
+                if cand not in seeds:
+                    seeds.append(cand)
+        if not seeds:
+            continue
+        row = tune_shape(*shape, rounds=rounds, only=seeds)
+        done[shape] = row
+        if row["results"]:
+            best = row["results"][0]
+            print(f"[playoff] {shape}: {len(seeds)} schedules, best {best['us']:.1f} us "
+                  f"({best['percentage_of_torch']:.0f}% of torch) {best['config']}", flush=True)
+        _write_done(done, out_path)
+
+
 def emit_table(results_paths: list[Path], table_path: Path, keep: tuple[int, ...] = (3,)) -> None:
     """Write the schedule table from one or more results files.  A shape present in several files takes
     its rows from the first file that has it; ``keep[i]`` schedules per shape are kept from file i
@@ -425,6 +474,9 @@ def main() -> None:
     parser.add_argument("--limit", type=int, default=0, help="corpus: only the N most frequent shapes (0 = all)")
     parser.add_argument("--light", action="store_true",
                         help="no eviction-hint pass and no sustained-regime pass (the broad corpus sweep)")
+    parser.add_argument("--playoff", default=None,
+                        help="comma-separated results files: time their fastest schedules against each other "
+                             "and write the ranking to --out")
     parser.add_argument("--worker", action="store_true", help=argparse.SUPPRESS)
     parser.add_argument("--shapes-file", default=None, help=argparse.SUPPRESS)
     args = parser.parse_args()
@@ -434,6 +486,10 @@ def main() -> None:
         return
     out = Path(args.out)
     out.parent.mkdir(parents=True, exist_ok=True)
+    if args.playoff:
+        playoff([Path(p) for p in args.playoff.split(",")], out, keep=int(args.emit_keep.split(",")[0]),
+                rounds=args.rounds)
+        return
     if args.worker:
         shapes = [tuple(s) for s in json.loads(Path(args.shapes_file).read_text())]
         measure(shapes, out, rounds=args.rounds, progress_path=out.with_suffix(".progress"), light=args.light)
