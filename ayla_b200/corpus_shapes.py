@@ -68,8 +68,8 @@ def pool(records: list[dict]) -> dict[tuple, dict]:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--from", dest="source", default="/root/reference/benchmarks",
-                        help="directory that holds the reference's two corpus files")
+    parser.add_argument("--from", dest="source", required=True,
+                        help="directory that holds the reference's two corpus files (its benchmarks/ folder)")
     parser.add_argument("--out", default=str(DEFAULT_OUT))
     args = parser.parse_args()
     records: list[dict] = []
