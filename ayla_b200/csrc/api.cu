@@ -311,6 +311,7 @@ int make_plan(const ayla_b200_config& c, int epilogue, int64_t batch, int64_t ro
   }
   plan->stream_k = 0;
   plan->kb_per_cta = 0;
+  plan->cluster_split = 0;  // also for the stream-K plan below, which returns before the cluster branch
   if (c.stream_k) {
     // Equal contiguous shares of the (tile, k-block) sequence; a share is never shorter
     // than four k-blocks so that a segment is worth its epilogue.
@@ -809,7 +810,7 @@ int ayla_b200_config_valid(const ayla_b200_config* cfg, int op, int dtype, int64
   if (rc) return rc;
   rc = check_config(*cfg, false);
   if (rc) return rc;
-  Plan plan;
+  Plan plan{};
   const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
   return make_plan(*cfg, epi, batch, cfg->swap_ab ? n : m, cfg->swap_ab ? m : n, k, 148, &plan);
 }
@@ -818,7 +819,7 @@ size_t ayla_b200_workspace_bytes(const ayla_b200_config* cfg, int op, int64_t ba
                                  int64_t n, int64_t k) {
   if (cfg == nullptr || check_config(*cfg, false) != AYLA_B200_OK) return 0;
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
-  Plan plan;
+  Plan plan{};
   const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
   if (make_plan(*cfg, epi, batch, cfg->swap_ab ? n : m, cfg->swap_ab ? m : n, k, 148, &plan)) return 0;
   return workspace_bytes_for(plan);
@@ -828,7 +829,7 @@ size_t ayla_b200_workspace_counter_bytes(const ayla_b200_config* cfg, int op, in
                                          int64_t m, int64_t n, int64_t k) {
   if (cfg == nullptr || check_config(*cfg, false) != AYLA_B200_OK) return 0;
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
-  Plan plan;
+  Plan plan{};
   const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
   if (make_plan(*cfg, epi, batch, cfg->swap_ab ? n : m, cfg->swap_ab ? m : n, k, 148, &plan)) return 0;
   return counter_bytes_for(plan);
@@ -923,7 +924,7 @@ static int gemm_fused(int op, int dtype, int activation, const void* bias, const
     pr.col_operand = bt;
   }
   const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
-  Plan plan;
+  Plan plan{};
   rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan, (activation != 0 || mul != nullptr) ? 1 : 0);
   if (rc) return rc;
   return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, bias, nullptr, out, m, n, workspace,
@@ -964,7 +965,7 @@ int ayla_b200_gemm_static_scratch(int op, int dtype, const void* bias, const voi
   pr.row_operand = c.swap_ab ? bt : a;
   pr.col_operand = c.swap_ab ? a : bt;
   const int epi = (op == AYLA_B200_OP_ADDMM) ? EPI_BIAS : EPI_PLAIN;
-  Plan plan;
+  Plan plan{};
   rc = make_plan(c, epi, batch, pr.rows, pr.cols, k, ds->sm_count, &plan);
   if (rc) return rc;
   const size_t need = workspace_bytes_for(plan);
@@ -1027,7 +1028,7 @@ int ayla_b200_swiglu(int dtype, const void* x, const void* w_gate, const void* w
   pr.batch = 1;
   pr.row_operand = x;
   pr.col_operand = w_gate;
-  Plan plan;
+  Plan plan{};
   rc = make_plan(c, EPI_SWIGLU, 1, m, n, k, ds->sm_count, &plan);
   if (rc) return rc;
   return launch_plan(plan, c, pr, dtype == AYLA_B200_BF16 ? 1 : 0, nullptr, w_up, out, m, n, nullptr, 0,

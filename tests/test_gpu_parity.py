@@ -222,6 +222,27 @@ def test_cluster_split_k_variants(split_k, device_state):
     assert torch.equal(first, again)
 
 
+@pytest.mark.parametrize("tile_n,cta_group", [(128, 1), (256, 1), (128, 2), (256, 2)])
+@pytest.mark.parametrize("grid_ctas", [0, 10, 36])
+def test_stream_k_variants(tile_n, cta_group, grid_ctas, device_state):
+    """Equal contiguous shares of the (tile, k-block) sequence per CTA: tiles cut between CTAs are
+    finished by the last contributor, summing in CTA order."""
+    torch.manual_seed(tile_n + cta_group + grid_ctas)
+    cfg = dict(tile_n=tile_n, cta_group=cta_group, stream_k=1, group_m=3, grid_ctas=grid_ctas)
+    for operation, dtype, batch, m, n, k in (("mm", "bfloat16", 1, 1024, 768, 520), ("addmm", "float16", 1, 300, 264, 1992),
+                                             ("bmm", "bfloat16", 3, 200, 136, 1024), ("mm", "float16", 1, 333, 520, 4104)):
+        assert _lib.config_valid(_lib.Config.from_dict(cfg), operation, dtype, batch, m, n, k), cfg
+        lead = (batch,) if operation == "bmm" else ()
+        a = torch.randn((*lead, m, k)).to(TD[dtype])
+        bt = (torch.randn((*lead, n, k)) * k ** -0.5).to(TD[dtype])
+        tensors = (a, bt) if operation != "addmm" else (torch.randn(n).to(TD[dtype]), a, bt)
+        out, status = run_abi(operation, dtype, tensors, cfg, device_state)
+        assert status == 0
+        assert_parity(out, O.gemm_ref32(operation, *tensors), f"{operation} {batch}x{m}x{n}x{k} {cfg}")
+        again, _ = run_abi(operation, dtype, tensors, cfg, device_state)
+        assert torch.equal(out, again)
+
+
 @pytest.mark.parametrize("split_k", [2, 4])
 @pytest.mark.parametrize("tile_n", [64, 128, 256])
 def test_paired_cluster_split_k_variants(split_k, tile_n, device_state):
