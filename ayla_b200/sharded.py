@@ -53,6 +53,32 @@ def m_panels(m: int, panel_rows: int) -> list[Panel]:
     return [Panel(r, min(panel_rows, m - r)) for r in range(0, m, panel_rows)]
 
 
+def fit_panel_rows(m: int, width: int, gemm_sms: int, tile_rows: int = 256, tile_cols: int = 256,
+                   min_fill: float = 0.95, max_panels: int = 24) -> int:
+    """Rows per M-panel such that a panel's output tiles fill a whole number of waves of the SMs the
+    GEMM may use (a 256-row tile occupies a CTA pair): the smallest such height that leaves at most
+    ``max_panels`` panels.  A panel of 2048 rows by 4096 columns is 128 tiles, 2.2 waves of 58 pairs
+    run as 3; 1792 rows are 112 tiles, 1.93 waves run as 2."""
+    pairs = max(1, gemm_sms // 2)
+    n_tiles = -(-width // tile_cols)
+    fallback, fallback_fill = max(tile_rows, -(-m // 16)), 0.0
+    for waves in range(1, 257):
+        row_tiles = (waves * pairs) // n_tiles
+        if row_tiles == 0:
+            continue
+        rows = row_tiles * tile_rows
+        if -(-m // rows) > max_panels:
+            continue
+        fill = row_tiles * n_tiles / (waves * pairs)
+        if fill >= min_fill:
+            return min(rows, -(-m // tile_rows) * tile_rows)
+        if fill > fallback_fill:
+            fallback, fallback_fill = rows, fill
+        if rows >= m:
+            break
+    return fallback
+
+
 def place_gathered_panel(out: torch.Tensor, gathered: torch.Tensor, panel: Panel) -> None:
     """``gathered`` is ``[g][panel.rows][N/g]`` (rank-major, as all-gather delivers it);
     write it to rows ``panel.row0 ..`` of the row-major ``out[M][N]``."""
@@ -197,10 +223,12 @@ class NShardedMM:
         self.rank = dist.get_rank(self.group)
         self.m, self.n, self.k, self.dtype = m, n, k, dtype
         self.col0, self.width = column_block(n, self.world, self.rank)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
         if panel_rows is None:
-            # Sixteen panels: only one sixteenth of the exchange is left uncovered by compute, and a
-            # panel is still several waves of tiles.
-            panel_rows = max(1024, -(-m // 16))
+            # Panels whose tiles fill whole waves of the SMs the GEMM keeps, at most 24 of them: only
+            # the last panel's exchange is left uncovered by compute.
+            reserved = reserve_sms if (exchange == "nccl" and self.world > 1) else 0
+            panel_rows = fit_panel_rows(m, self.width, sms - reserved)
         self.panels = m_panels(m, panel_rows)
         self.plan = overlap_plan(len(self.panels), exchange)
         self.device = device
@@ -209,7 +237,6 @@ class NShardedMM:
         torch_dtype = _TORCH_DTYPES[dtype]
         self.torch_dtype = torch_dtype
         rows = self.panels[0].rows
-        sms = torch.cuda.get_device_properties(device).multi_processor_count
         # One schedule per distinct panel height (the last panel may be short); the workspace is
         # sized for the largest need.
         self.cfgs: dict[int, object] = {}
@@ -487,29 +514,36 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
     sweep = []
     # (NCCL thread blocks, SMs left free): NCCL's blocks are small enough to share an SM, so fewer SMs than
     # blocks may be set aside.
-    choices = ((32, 32), (32, 16), (48, 16), (64, 16), (64, 24)) if world > 2 else ((16, 16),)
-    for max_ctas, reserve in choices:
+    # The third entry is the panel height: None = fitted to whole waves of the SMs the GEMM keeps.
+    choices = (((32, 32, None), (32, 32, 2048), (48, 48, None), (32, 16, None), (64, 24, None)) if world > 2
+               else ((16, 16, None), (16, 16, 2048)))
+    for max_ctas, reserve, rows in choices:
         try:
-            row = run_variant(f"nccl max_ctas={max_ctas} reserve={reserve}", "nccl", max_ctas=max_ctas, reserve_sms=reserve)
+            row = run_variant(f"nccl max_ctas={max_ctas} reserve={reserve} rows={rows}", "nccl", max_ctas=max_ctas,
+                              reserve_sms=reserve, panel_rows=rows)
+            row["panel_rows"] = rows
             sweep.append(row)
         except SystemExit:
             raise
         except Exception as exc:  # noqa: BLE001 - reported, not fatal for the headline line
-            sweep.append({"nccl_max_ctas": max_ctas, "reserve_sms": reserve, "error": f"{type(exc).__name__}: {exc}"})
+            sweep.append({"nccl_max_ctas": max_ctas, "reserve_sms": reserve, "panel_rows": rows,
+                          "error": f"{type(exc).__name__}: {exc}"})
     good = [r for r in sweep if "ms" in r]
     if good:
         best = min(good, key=lambda r: r["ms"])
         try:
             results["mm32768"] = run_variant("nccl best", "nccl", max_ctas=best["nccl_max_ctas"],
-                                             reserve_sms=best["reserve_sms"], legs=True)
+                                             reserve_sms=best["reserve_sms"], panel_rows=best["panel_rows"], legs=True)
         except SystemExit:
             raise
         except Exception as exc:  # noqa: BLE001
             results["mm32768"] = {"error": f"{type(exc).__name__}: {exc}"}
-        results["mm32768_sweep"] = [{k: r.get(k) for k in ("nccl_max_ctas", "reserve_sms", "ms", "speedup_vs_one_gpu", "error")}
+        results["mm32768_sweep"] = [{k: r.get(k) for k in ("nccl_max_ctas", "reserve_sms", "panel_rows", "partition", "ms",
+                                                           "speedup_vs_one_gpu", "error")}
                                     for r in sweep]
         for key, kwargs in (("mm32768_blocked_layout", dict(exchange="nccl", layout="blocked",
-                                                            max_ctas=best["nccl_max_ctas"], reserve_sms=best["reserve_sms"])),
+                                                            max_ctas=best["nccl_max_ctas"], reserve_sms=best["reserve_sms"],
+                                                            panel_rows=best["panel_rows"])),
                             ("mm32768_dma", dict(exchange="dma"))):
             try:
                 results[key] = run_variant(key, **kwargs)

@@ -35,6 +35,22 @@ def test_column_blocks_and_panels():
     assert [(p.row0, p.rows) for p in panels] == [(0, 4096), (4096, 4096), (8192, 1808)]
 
 
+def test_panel_height_is_fitted_to_whole_waves_of_the_sms_the_gemm_keeps():
+    """A 256-row tile occupies a CTA pair: with 32 SMs left to NCCL, 58 pairs take the 16 column tiles
+    of 7 row tiles (112 tiles) in two waves; 2048 rows (128 tiles) would need three."""
+    assert sharded.fit_panel_rows(32768, 4096, 148 - 32) == 7 * 256
+    assert sharded.fit_panel_rows(32768, 4096, 148) == 9 * 256           # 144 of 148 pair slots in two waves
+    for m, width, sms in ((32768, 4096, 116), (32768, 16384, 132), (16384, 8192, 132), (32768, 4096, 100)):
+        rows = sharded.fit_panel_rows(m, width, sms)
+        tiles = (rows // 256) * -(-width // 256)
+        waves = -(-tiles // (sms // 2))
+        assert rows % 256 == 0 and tiles / (waves * (sms // 2)) >= 0.95
+        assert len(sharded.m_panels(m, rows)) <= 24
+    # small problems: one panel, never taller than the matrix rounded up to a tile
+    assert sharded.fit_panel_rows(1000, 512, 148) == 1024
+    assert len(sharded.m_panels(1000, sharded.fit_panel_rows(1000, 512, 148))) == 1
+
+
 def test_place_gathered_panel_unpermutes():
     out = torch.zeros(6, 8)
     gathered = torch.arange(2 * 3 * 4, dtype=torch.float32).view(2, 3, 4)
