@@ -208,7 +208,7 @@ class NShardedMM:
     """
 
     def __init__(self, m: int, n: int, k: int, dtype: str, device: torch.device, group=None,
-                 panel_rows: int | None = None, reserve_sms: int = 16, exchange: str = "nccl",
+                 panel_rows: int | str | None = None, reserve_sms: int = 16, exchange: str = "nccl",
                  layout: str = "row_major"):
         from . import _lib
         from .gemm_jit import _TORCH_DTYPES, select_gemm_schedule
@@ -224,9 +224,14 @@ class NShardedMM:
         self.m, self.n, self.k, self.dtype = m, n, k, dtype
         self.col0, self.width = column_block(n, self.world, self.rank)
         sms = torch.cuda.get_device_properties(device).multi_processor_count
-        if panel_rows is None:
-            # Panels whose tiles fill whole waves of the SMs the GEMM keeps, at most 24 of them: only
-            # the last panel's exchange is left uncovered by compute.
+        if panel_rows is None and exchange == "nccl":
+            # Sixteen panels: only one sixteenth of the exchange is left uncovered by compute, and a
+            # panel is still several waves of tiles.  (The all-gather, not the GEMM, bounds this path
+            # at 8 GPUs: panels fitted to whole waves made the GEMM leg shorter and the whole longer,
+            # 9.09 against 8.67 ms for 32768^3, because there were 19 gathers instead of 16.)
+            panel_rows = max(1024, -(-m // 16))
+        elif panel_rows is None or panel_rows == "fit":
+            # Panels whose tiles fill whole waves of the SMs the GEMM keeps.
             reserved = reserve_sms if (exchange == "nccl" and self.world > 1) else 0
             panel_rows = fit_panel_rows(m, self.width, sms - reserved)
         self.panels = m_panels(m, panel_rows)
@@ -514,9 +519,9 @@ def bench_sharded(rank: int, world: int, device: torch.device, steps: int = 5) -
     sweep = []
     # (NCCL thread blocks, SMs left free): NCCL's blocks are small enough to share an SM, so fewer SMs than
     # blocks may be set aside.
-    # The third entry is the panel height: None = fitted to whole waves of the SMs the GEMM keeps.
-    choices = (((32, 32, None), (32, 32, 2048), (48, 48, None), (32, 16, None), (64, 24, None)) if world > 2
-               else ((16, 16, None), (16, 16, 2048)))
+    # The third entry is the panel height: None = sixteen panels, "fit" = whole waves of the SMs the GEMM keeps.
+    choices = (((32, 32, None), (32, 32, "fit"), (48, 48, None), (32, 16, None), (64, 24, None)) if world > 2
+               else ((16, 16, None), (16, 16, "fit")))
     for max_ctas, reserve, rows in choices:
         try:
             row = run_variant(f"nccl max_ctas={max_ctas} reserve={reserve} rows={rows}", "nccl", max_ctas=max_ctas,
