@@ -364,7 +364,7 @@ def measure_isolated(shapes, out_path: Path, shapes_file: Path, rounds: int = 3,
         print(f"[autotune] {stuck}: {reason}; restarting the worker", flush=True)
 
 
-def playoff(results_paths: list[Path], out_path: Path, keep: int = 3, rounds: int = 5) -> None:
+def playoff(results_paths: list[Path], out_path: Path, keep: int = 3, rounds: int = 5, limit: int = 0) -> None:
     """Time the ``keep`` fastest schedules of every results file against each other, shape by shape in
     the first file's order, and write the ranking to ``out_path`` (same format, resumable): two sweeps
     of the same shape, run at different times, rank close schedules differently, and their own times
@@ -372,7 +372,9 @@ def playoff(results_paths: list[Path], out_path: Path, keep: int = 3, rounds: in
     _lib.init(torch.cuda.current_device())
     sweeps = [_load_done(path) for path in results_paths]
     done = _load_done(out_path)
-    for shape in sweeps[0]:
+    for index, shape in enumerate(sweeps[0]):
+        if limit and index >= limit:
+            break
         if shape in done:
             continue
         seeds: list[dict] = []
@@ -471,7 +473,7 @@ def main() -> None:
     parser.add_argument("--emit-keep", default="3", help="schedules kept per shape, per results file (comma separated)")
     parser.add_argument("--isolate", action="store_true", help="measure in a supervised worker process")
     parser.add_argument("--rounds", type=int, default=5)
-    parser.add_argument("--limit", type=int, default=0, help="corpus: only the N most frequent shapes (0 = all)")
+    parser.add_argument("--limit", type=int, default=0, help="corpus, play-off: only the first N shapes (0 = all)")
     parser.add_argument("--light", action="store_true",
                         help="no eviction-hint pass and no sustained-regime pass (the broad corpus sweep)")
     parser.add_argument("--playoff", default=None,
@@ -488,7 +490,7 @@ def main() -> None:
     out.parent.mkdir(parents=True, exist_ok=True)
     if args.playoff:
         playoff([Path(p) for p in args.playoff.split(",")], out, keep=int(args.emit_keep.split(",")[0]),
-                rounds=args.rounds)
+                rounds=args.rounds, limit=args.limit)
         return
     if args.worker:
         shapes = [tuple(s) for s in json.loads(Path(args.shapes_file).read_text())]
