@@ -122,6 +122,16 @@ def _waves(config: dict[str, object], batch: int, m: int, n: int) -> int:
     return -(-units // (_SM_COUNT // pair))
 
 
+def _column_padding(config: dict[str, object], m: int, n: int) -> float:
+    """Share of a schedule's tile columns that lie past the matrix on this shape (the swapped form
+    tiles the token dimension): a 128-column tile on 64 output columns computes half of itself for
+    nothing, however well it did where it was measured on 128."""
+    cols = m if config["swap_ab"] else n
+    tile = int(config["tile_n"])
+    padded = -(-cols // tile) * tile
+    return (padded - cols) / padded
+
+
 def measured_gemm_configs(operation: str, dtype: str, m: int, n: int, k: int,
                           batch: int = 1) -> tuple[dict[str, object], ...]:
     """All schedules measured on exactly this shape, winner first, as fresh copies."""
@@ -158,6 +168,10 @@ def select_gemm_schedule(operation: str, dtype: str, m: int, n: int, k: int,
             captured = {**_DEFAULTS, **CONFIGS[index]}
             if shape != query and _waves(captured, batch, m, n) > _waves(captured, shape[0], shape[1], shape[2]):
                 continue  # it would no longer fit the number of waves it was measured at
+            if shape != query:
+                waste = _column_padding(captured, m, n)
+                if waste >= 0.34 and waste > _column_padding(captured, shape[1], shape[2]) + 0.2:
+                    continue  # its tiles would be a third or more padding here and were not where it was measured
             seed = _seed(captured, operation, dtype, m, n, k, batch, shape, exact=shape == query)
             if seed is not None:
                 if shape not in SCHEDULES.get((operation, dtype), {}):

@@ -298,3 +298,16 @@ def test_launcher_gives_every_stream_its_own_k_split_workspace(monkeypatch):
     current_stream[0], capturing[0] = 9, True
     with pytest.raises(RuntimeError, match="graph capture"):
         launcher(tensor, tensor, tensor)
+
+
+def test_a_schedule_is_not_transferred_to_a_shape_where_its_tiles_are_mostly_padding():
+    from ayla_b200 import gemm_jit
+
+    wide = {**gemm_jit._DEFAULTS, "tile_n": 128, "cta_group": 2}
+    assert gemm_jit._column_padding(wide, 4096, 128) == 0.0
+    assert gemm_jit._column_padding(wide, 4096, 64) == 0.5            # half of every tile lies past the matrix
+    swapped = {**gemm_jit._DEFAULTS, "tile_n": 64, "swap_ab": 1}
+    assert gemm_jit._column_padding(swapped, 24, 4096) == pytest.approx(40 / 64)   # the swapped form tiles the tokens
+    # whatever the table holds near it, a 64-column output never gets a schedule wider than it needs twice over
+    seed = gemm_jit.select_gemm_schedule("mm", "bfloat16", 401536, 64, 512)
+    assert seed is not None and gemm_jit._column_padding({**gemm_jit._DEFAULTS, **seed.builder_config}, 401536, 64) < 0.34
